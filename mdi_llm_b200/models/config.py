@@ -19,7 +19,7 @@ from typing import Any, Dict, Optional, Union
 
 import yaml
 
-__all__ = ["Config", "GPTConfig", "find_multiple"]
+__all__ = ["Config", "GPTConfig", "HybridConfig", "find_multiple"]
 
 
 def find_multiple(n: int, k: int) -> int:
@@ -203,3 +203,107 @@ def GPTConfig(block_size: int = 1024, vocab_size: int = 50304, n_layer: int = 12
                   padded_vocab_size=vocab_size, n_layer=n_layer, n_head=n_head, n_embd=n_embd, rotary_percentage=0.0,
                   parallel_residual=False, bias=bias, norm_class_name="LayerNorm", mlp_class_name="GptNeoxMLP",
                   gelu_approximate="tanh", pos_embedding="learned", tie_embeddings=True, **extra)
+
+
+# =============================================================================================
+# hybrid family: a list of heterogeneous layers (attention and recurrent mixers) read from config.json
+# =============================================================================================
+MIXER_KEYS = {
+    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "scale", "rot"),
+    "gla": ("heads", "dim", "vdim", "tau"),
+    "channel_delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
+}
+
+
+@dataclass
+class HybridConfig:
+    """A decoder whose layers each name their own mixer and sizes (``config.json`` of the hybrid family).
+
+    ``layers[i] = {"type": <mixer kind>, "mixer": {...sizes...}, "mlp": {"kind": "dense", "ff": n} | None}``.
+    ``loop = {"start", "stop", "times"}`` repeats layers ``start..stop-1`` ``times`` times with shared weights and a
+    state of its own per pass; each pass starts with a re-injection of the embedding output.  Everything a model
+    of the family may vary is a field; nothing is assumed from a particular checkpoint.
+    """
+
+    architecture: str = "Badapel"
+    vocab: int = 0
+    width: int = 0
+    layers: list = field(default_factory=list)
+    loop: Optional[dict] = None
+    norm_eps: float = 1e-6
+    logit_softcap: float = 0.0
+    name: str = ""
+
+    def __post_init__(self) -> None:
+        if self.vocab <= 0 or self.width <= 0 or not self.layers:
+            raise ValueError("a hybrid config needs vocab, width and at least one layer")
+        for i, spec in enumerate(self.layers):
+            kind = spec.get("type")
+            if kind not in MIXER_KEYS:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            missing = [k for k in MIXER_KEYS[kind] if k not in spec.get("mixer", {})]
+            if missing:
+                raise ValueError(f"layer {i} ({kind}): missing mixer fields {missing}")
+            mlp = spec.get("mlp")
+            if mlp is not None and mlp.get("kind") != "dense":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        if self.loop is not None:
+            a, b, t = self.loop["start"], self.loop["stop"], self.loop["times"]
+            if not (0 <= a < b <= len(self.layers)) or t < 1:
+                raise ValueError(f"bad loop {self.loop}")
+        if not self.name:
+            self.name = self.architecture
+
+    @property
+    def n_layer(self) -> int:
+        return len(self.layers)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def padded_vocab_size(self) -> int:
+        return self.vocab
+
+    def layer_runs(self) -> list:
+        """Execution order as ``(layer index, starts a pass)``; a looped layer appears once per pass."""
+        n = len(self.layers)
+        if self.loop is None:
+            return [(i, False) for i in range(n)]
+        a, b, times = self.loop["start"], self.loop["stop"], self.loop["times"]
+        runs = [(i, False) for i in range(a)]
+        for _ in range(times):
+            runs += [(i, i == a) for i in range(a, b)]
+        return runs + [(i, False) for i in range(b, n)]
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "HybridConfig":
+        return cls(architecture=d.get("architecture", "Badapel"), vocab=int(d["vocab"]), width=int(d["width"]),
+                   layers=[dict(x) for x in d["layers"]], loop=dict(d["loop"]) if d.get("loop") else None,
+                   norm_eps=float(d.get("norm", {}).get("eps", 1e-6)),
+                   logit_softcap=float(d.get("logit_softcap") or 0.0), name=d.get("name", ""))
+
+    @classmethod
+    def from_file(cls, path: Union[str, Path]) -> "HybridConfig":
+        import json
+
+        with open(path, encoding="utf-8") as fp:
+            return cls.from_dict(json.load(fp))
+
+    def asdict(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                               "layers": self.layers, "norm": {"eps": self.norm_eps}}
+        if self.loop is not None:
+            out["loop"] = self.loop
+        if self.logit_softcap:
+            out["logit_softcap"] = self.logit_softcap
+        return out
+
+    def save(self, checkpoint_dir: Union[str, Path]) -> Path:
+        import json
+
+        p = Path(checkpoint_dir) / "config.json"
+        with open(p, "w", encoding="utf-8") as fp:
+            json.dump(self.asdict(), fp, indent=1)
+        return p

@@ -1,0 +1,435 @@
+"""The hybrid model family: a residual stream through layers that each pick their own sequence mixer.
+
+Mixers (all written against the packed-batch operations of :mod:`mdi_llm_b200.ops.hybrid`):
+
+* :class:`LatentAttention` — softmax attention whose keys and values are expansions of one cached latent row per
+  token plus a rotated key part shared by the heads.  Only that row is cached; the query is carried into the latent
+  space (``q W_uk``) so that the attention kernel reads the cache directly, and the attended latent is expanded
+  by ``W_uv`` afterwards.
+* :class:`GatedLinearAttention` — ``S_t = diag(a_t) S_(t-1) + k_t v_t^T`` with a data-dependent decay per key
+  channel.
+* :class:`ChannelDelta` — the gated delta rule with a decay per key channel, short causal convolutions on q, k, v
+  and unit-norm q, k.
+
+A layer is a *sandwich* block: ``x += norm_b(f(norm_a(x)))`` for the mixer and again for the feed-forward, with
+the residual stream kept in fp32.  A span of layers may be looped; each pass owns its own state and starts by
+mixing the embedding output back in.  State lives in a :class:`StatePool` — slots like the KV pool of the
+transformer family (``models/gpt.py:KVPool``), one entry per *layer run*.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+import torch.nn as nn
+
+from ..ops import hybrid as H
+from .config import HybridConfig
+
+__all__ = ["HybridLM", "StatePool", "SandwichBlock", "LatentAttention", "GatedLinearAttention", "ChannelDelta",
+           "DenseFF", "read_safetensors", "write_safetensors", "load_hybrid"]
+
+_ST_DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32, "I64": torch.int64}
+
+
+def read_safetensors(path: Union[str, Path]) -> Dict[str, torch.Tensor]:
+    """Minimal reader: 8-byte little-endian header length, JSON header, raw little-endian data."""
+    raw = Path(path).read_bytes()
+    (n,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + n])
+    out: Dict[str, torch.Tensor] = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = info["data_offsets"]
+        dt = _ST_DTYPES[info["dtype"]]
+        buf = bytearray(raw[8 + n + a:8 + n + b])
+        out[name] = (torch.frombuffer(buf, dtype=dt) if buf else torch.empty(0, dtype=dt)).view(info["shape"])
+    return out
+
+
+def write_safetensors(tensors: Dict[str, torch.Tensor], path: Union[str, Path]) -> None:
+    names = {v: k for k, v in _ST_DTYPES.items()}
+    header: Dict[str, Any] = {}
+    blobs, off = [], 0
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        b = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(path, "wb") as fp:
+        fp.write(struct.pack("<Q", len(hj)))
+        fp.write(hj)
+        for b in blobs:
+            fp.write(b)
+
+
+# =============================================================================================
+# state
+# =============================================================================================
+class StatePool:
+    """Slots of per-sequence state for every layer run of a hybrid model.
+
+    A run of a latent-attention layer owns ``cache [slots, max_seq, kv_rank + rot_dim]`` (activation type); a run
+    of a recurrent layer owns ``state [slots, heads, dim, vdim]`` in fp32 and, with a short convolution,
+    ``conv [slots, taps - 1, channels]``.  ``alloc`` hands out a slot with zeroed recurrent and convolution state
+    (attention rows need no clearing: a row is written before any query can see it); ``free`` returns it.
+    The pool grows (doubling, contents kept) when more slots are asked for than it has.
+    """
+
+    def __init__(self, config: HybridConfig, n_slots: int, max_seq_length: int, device: torch.device, dtype: torch.dtype) -> None:
+        self.config, self.max_seq_length, self.device, self.dtype = config, int(max_seq_length), device, dtype
+        self.n_slots = 0
+        self.runs: List[Dict[str, torch.Tensor]] = [{} for _ in config.layer_runs()]
+        self.free_slots: List[int] = []
+        self.length: Dict[int, int] = {}
+        self._grow(max(1, n_slots))
+
+    def _shapes(self, spec: Dict[str, Any]) -> Dict[str, Tuple[Tuple[int, ...], torch.dtype]]:
+        m = spec["mixer"]
+        if spec["type"] == "latent_attention":
+            return {"cache": ((self.max_seq_length, m["kv_rank"] + m["rot_dim"]), self.dtype)}
+        out = {"state": ((m["heads"], m["dim"], m["vdim"]), torch.float32)}
+        if spec["type"] == "channel_delta" and m["conv"] > 1:
+            ch = 2 * m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"]
+            out["conv"] = ((m["conv"] - 1, ch), self.dtype)
+        return out
+
+    def _grow(self, n_slots: int) -> None:
+        for run, (li, _) in zip(self.runs, self.config.layer_runs()):
+            for key, (shape, dt) in self._shapes(self.config.layers[li]).items():
+                new = torch.zeros((n_slots, *shape), device=self.device, dtype=dt)
+                if key in run:
+                    new[: self.n_slots] = run[key]
+                run[key] = new
+        self.free_slots += list(range(self.n_slots, n_slots))
+        self.n_slots = n_slots
+
+    def alloc(self) -> int:
+        if not self.free_slots:
+            self._grow(2 * self.n_slots)
+        slot = self.free_slots.pop(0)
+        for run in self.runs:
+            for key in ("state", "conv"):
+                if key in run:
+                    run[key][slot].zero_()
+        self.length[slot] = 0
+        return slot
+
+    def free(self, slot: int) -> None:
+        if slot not in self.length:
+            raise KeyError(f"slot {slot} is not in use")
+        del self.length[slot]
+        self.free_slots.append(slot)
+
+    @property
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for run in self.runs for t in run.values())
+
+
+# =============================================================================================
+# modules
+# =============================================================================================
+def _param(*shape: int) -> nn.Parameter:
+    return nn.Parameter(torch.empty(*shape), requires_grad=False)
+
+
+class _Fused:
+    """Mixin: several projections that read the same input become one weight; the originals turn into row views."""
+
+    def fuse(self, names: Sequence[str]) -> None:
+        ws = [getattr(self, n) for n in names]
+        fused = torch.cat([w.data for w in ws], 0).contiguous()
+        self.w_in = fused
+        self.cols: Dict[str, Tuple[int, int]] = {}
+        r = 0
+        for n, w in zip(names, ws):
+            self.cols[n] = (r, r + w.size(0))
+            w.data = fused[r:r + w.size(0)]
+            r += w.size(0)
+
+    def col(self, p: torch.Tensor, name: str) -> torch.Tensor:
+        a, b = self.cols[name]
+        return p[:, a:b]
+
+
+class LatentAttention(nn.Module, _Fused):
+    tensor_names = {"dq": "dq", "dq.norm": "dq_norm", "uq": "uq", "dkv": "dkv", "dkv.norm": "dkv_norm", "uk": "uk",
+                    "uv": "uv", "g": "g", "o": "o"}
+
+    def __init__(self, width: int, m: Dict[str, Any], eps: float) -> None:
+        super().__init__()
+        self.H, self.D, self.R, self.V = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
+        self.L, self.QR, self.scale, self.eps = m["kv_rank"], m["q_rank"], float(m["scale"]), eps
+        self.nrot, self.rot_base = int(m["rot"]["dims"]), float(m["rot"]["base"])
+        if self.nrot > self.R or self.nrot % 2:
+            raise ValueError("rot.dims must be even and at most rot_dim")
+        H_, D, R, V, L = self.H, self.D, self.R, self.V, self.L
+        self.dq, self.dq_norm, self.uq = _param(self.QR, width), _param(self.QR), _param(H_ * (D + R), self.QR)
+        self.dkv, self.dkv_norm = _param(L + R, width), _param(L)
+        self.uk, self.uv = _param(H_ * D, L), _param(H_ * V, L)
+        self.g, self.o = _param(H_ * V, width), _param(width, H_ * V)
+        self.inv_freq: Optional[torch.Tensor] = None
+
+    def finalize(self) -> None:
+        self.fuse(("dq", "dkv", "g"))
+        self.inv_freq = H.rotary_inv_freq(self.nrot, self.rot_base, self.dq.device)
+
+    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
+        N = h.size(0)
+        Hh, D, R, V, L = self.H, self.D, self.R, self.V, self.L
+        p = H.linear(h, self.w_in)
+        cq = H.norm_rows(self.col(p, "dq"), self.dq_norm, None, self.eps, "rms", h.dtype)
+        q = H.linear(cq, self.uq)
+        H.latent_append(self.col(p, "dkv"), q, self.dkv_norm, self.inv_freq, st["cache"], plan, Hh, D, R, L, self.nrot, self.eps)
+        qlat = torch.bmm(q.view(N, Hh, D + R)[:, :, :D].transpose(0, 1), self.uk.view(Hh, D, L)).contiguous()
+        olat = H.latent_attn(qlat, q, st["cache"], plan, Hh, D, R, L, self.scale)
+        o = torch.bmm(olat, self.uv.view(Hh, V, L).transpose(1, 2)).contiguous()
+        return H.linear(H.headmajor_gate(o, self.col(p, "g")), self.o)
+
+
+class GatedLinearAttention(nn.Module, _Fused):
+    tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2", "a2.b": "a2_b"}
+
+    def __init__(self, width: int, m: Dict[str, Any], eps: float, rank: int) -> None:
+        super().__init__()
+        self.H, self.D, self.V, self.tau, self.eps = m["heads"], m["dim"], m["vdim"], float(m["tau"]), eps
+        Hh, D, V = self.H, self.D, self.V
+        self.q, self.k, self.v, self.g = _param(Hh * D, width), _param(Hh * D, width), _param(Hh * V, width), _param(Hh * V, width)
+        self.o, self.norm = _param(width, Hh * V), _param(V)
+        self.a1, self.a2, self.a2_b = _param(rank, width), _param(Hh * D, rank), _param(Hh * D)
+
+    def finalize(self) -> None:
+        self.fuse(("q", "k", "v", "g", "a1"))
+
+    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
+        p = H.linear(h, self.w_in)
+        z = H.linear(self.col(p, "a1"), self.a2)
+        y = H.gated_recurrence(self.col(p, "q"), self.col(p, "k"), self.col(p, "v"), z, self.col(p, "g"), self.norm,
+                               st["state"], plan, heads=self.H, kv_heads=self.H, dim=self.D, vdim=self.V, mode="gla",
+                               eps=self.eps, zb=self.a2_b, tau=self.tau)
+        return H.linear(y, self.o)
+
+
+class ChannelDelta(nn.Module, _Fused):
+    tensor_names = {"q": "q", "q.conv": "q_conv", "k": "k", "k.conv": "k_conv", "v": "v", "v.conv": "v_conv", "b": "b",
+                    "A_log": "A_log", "norm": "norm", "a1": "a1", "a2": "a2", "dt_bias": "dt_bias", "g1": "g1", "g2": "g2",
+                    "o": "o"}
+
+    def __init__(self, width: int, m: Dict[str, Any], eps: float, rank_a: int, rank_g: int) -> None:
+        super().__init__()
+        self.H, self.G, self.D, self.V, self.taps, self.eps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], eps
+        if self.H % self.G:
+            raise ValueError("heads must be a multiple of kv_heads")
+        Hh, G, D, V, taps = self.H, self.G, self.D, self.V, self.taps
+        self.q, self.k, self.v = _param(G * D, width), _param(G * D, width), _param(Hh * V, width)
+        self.q_conv, self.k_conv, self.v_conv = _param(G * D, taps), _param(G * D, taps), _param(Hh * V, taps)
+        self.b, self.A_log, self.norm = _param(Hh, width), _param(Hh), _param(V)
+        self.a1, self.a2, self.dt_bias = _param(rank_a, width), _param(Hh * D, rank_a), _param(Hh * D)
+        self.g1, self.g2, self.o = _param(rank_g, width), _param(Hh * V, rank_g), _param(width, Hh * V)
+
+    def finalize(self) -> None:
+        self.fuse(("q", "k", "v", "b", "a1", "g1"))
+        self.conv_w = torch.cat((self.q_conv.data, self.k_conv.data, self.v_conv.data), 0).contiguous()
+
+    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
+        GD, HV = self.G * self.D, self.H * self.V
+        p = H.linear(h, self.w_in)
+        if self.taps > 1:
+            c = H.conv_silu(p[:, :2 * GD + HV], self.conv_w, st["conv"], plan)
+        else:
+            c = H.conv_silu(p[:, :2 * GD + HV], self.conv_w, p.new_zeros(1, 0, 2 * GD + HV), plan)
+        z = H.linear(self.col(p, "a1"), self.a2)
+        gate = H.linear(self.col(p, "g1"), self.g2)
+        y = H.gated_recurrence(c[:, :GD], c[:, GD:2 * GD], c[:, 2 * GD:], z, gate, self.norm, st["state"], plan,
+                               heads=self.H, kv_heads=self.G, dim=self.D, vdim=self.V, mode="delta", eps=self.eps,
+                               zb=self.dt_bias, beta=self.col(p, "b"), a_log=self.A_log)
+        return H.linear(y, self.o)
+
+
+class DenseFF(nn.Module):
+    tensor_names = {"up": "up", "down": "down"}
+
+    def __init__(self, width: int, ff: int) -> None:
+        super().__init__()
+        self.up, self.down = _param(ff, width), _param(width, ff)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return H.linear(H.gelu_(H.linear(h, self.up)), self.down)
+
+
+class _LN(nn.Module):
+    def __init__(self, width: int) -> None:
+        super().__init__()
+        self.w, self.b = _param(width), _param(width)
+
+
+class SandwichBlock(nn.Module):
+    """``x += norm1b(mixer(norm1(x)))``, then ``x += norm2b(ff(norm2(x)))`` when the layer has a feed-forward."""
+
+    def __init__(self, width: int, mixer: nn.Module, ff: Optional[nn.Module], eps: float) -> None:
+        super().__init__()
+        self.mix, self.mlp, self.eps = mixer, ff, eps
+        self.norm1, self.norm1b = _LN(width), _LN(width)
+        if ff is not None:
+            self.norm2, self.norm2b = _LN(width), _LN(width)
+
+    def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
+        h = H.norm_rows(x, self.norm1.w, self.norm1.b, self.eps, "layer", dtype)
+        H.norm_accumulate(x, self.mix(h, plan, st), self.norm1b.w, self.norm1b.b, self.eps)
+        if self.mlp is not None:
+            h = H.norm_rows(x, self.norm2.w, self.norm2.b, self.eps, "layer", dtype)
+            H.norm_accumulate(x, self.mlp(h), self.norm2b.w, self.norm2b.b, self.eps)
+
+
+def _rank_of(tensors: Optional[Dict[str, torch.Tensor]], key: str, default: int) -> int:
+    return int(tensors[key].shape[0]) if tensors is not None and key in tensors else default
+
+
+class HybridLM(nn.Module):
+    """Embedding -> layer runs (with an optional looped span) -> final norm -> tied head -> soft cap.
+
+    ``forward`` runs ONE step of a packed batch against a :class:`StatePool`; it is the step function for prompts
+    and decoding alike.  Low-rank side projections (decay and gate bottlenecks) take their rank from the
+    checkpoint's tensor shapes (``ranks``), since the configuration does not name them.
+    """
+
+    def __init__(self, config: HybridConfig, ranks: Optional[Dict[str, int]] = None) -> None:
+        super().__init__()
+        self.config = config
+        ranks = ranks or {}
+        C, eps = config.width, config.norm_eps
+        self.embed = _param(config.vocab, C)
+        self.loop_in = _param(C, 2 * C) if config.loop is not None else None
+        blocks = []
+        for i, spec in enumerate(config.layers):
+            m, kind = spec["mixer"], spec["type"]
+            if kind == "latent_attention":
+                mixer: nn.Module = LatentAttention(C, m, eps)
+            elif kind == "gla":
+                mixer = GatedLinearAttention(C, m, eps, ranks.get(f"l{i}.mix.a1", 16))
+            else:
+                mixer = ChannelDelta(C, m, eps, ranks.get(f"l{i}.mix.a1", 16), ranks.get(f"l{i}.mix.g1", 16))
+            ff = DenseFF(C, spec["mlp"]["ff"]) if spec.get("mlp") else None
+            blocks.append(SandwichBlock(C, mixer, ff, eps))
+        self.blocks = nn.ModuleList(blocks)
+        self.final_norm = _LN(C)
+        self.runs = config.layer_runs()
+
+    # ---- weights -------------------------------------------------------------------------------
+    def tensor_map(self) -> Dict[str, nn.Parameter]:
+        """Checkpoint tensor name -> parameter."""
+        out: Dict[str, nn.Parameter] = {"embed": self.embed, "final.norm": self.final_norm.w, "final.norm.b": self.final_norm.b}
+        if self.loop_in is not None:
+            out["loop.in"] = self.loop_in
+        for i, blk in enumerate(self.blocks):
+            norms = ["norm1", "norm1b"] + (["norm2", "norm2b"] if blk.mlp is not None else [])
+            for n in norms:
+                out[f"l{i}.{n}"] = getattr(blk, n).w
+                out[f"l{i}.{n}.b"] = getattr(blk, n).b
+            for short, attr in blk.mix.tensor_names.items():
+                out[f"l{i}.mix.{short}"] = getattr(blk.mix, attr)
+            if blk.mlp is not None:
+                for short, attr in blk.mlp.tensor_names.items():
+                    out[f"l{i}.mlp.{short}"] = getattr(blk.mlp, attr)
+        return out
+
+    def load_tensors(self, tensors: Dict[str, torch.Tensor], device: Union[str, torch.device], dtype: torch.dtype) -> "HybridLM":
+        tm = self.tensor_map()
+        missing, extra = sorted(set(tm) - set(tensors)), sorted(set(tensors) - set(tm))
+        if missing or extra:
+            raise KeyError(f"checkpoint does not match the configuration: missing {missing[:5]}, unexpected {extra[:5]}")
+        for name, p in tm.items():
+            t = tensors[name]
+            if tuple(t.shape) != tuple(p.shape):
+                raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != expected {tuple(p.shape)}")
+            p.data = t.to(device=device, dtype=dtype).contiguous()
+        return self.finalize()
+
+    def init_random(self, device: Union[str, torch.device], dtype: torch.dtype, seed: int = 0, std: float = 0.02) -> "HybridLM":
+        """Random weights (benchmarks and tests): projections N(0, std * sqrt(width / fan_in)), norm weights near 1."""
+        gen = torch.Generator().manual_seed(seed)
+        for name, p in self.tensor_map().items():
+            if p.dim() == 2 and not name.endswith(".conv"):
+                t = torch.randn(p.shape, generator=gen) * (p.shape[1] ** -0.5)
+            elif name.endswith(".conv"):
+                t = torch.randn(p.shape, generator=gen) * 0.5
+            elif name.endswith(".b") and p.dim() == 1 and "norm" in name:
+                t = torch.randn(p.shape, generator=gen) * 0.1
+            elif "norm" in name:
+                t = 1.0 + torch.randn(p.shape, generator=gen) * 0.1
+            else:
+                t = torch.randn(p.shape, generator=gen) * 0.5
+            if name == "embed":
+                t = torch.randn(p.shape, generator=gen)
+            p.data = t.to(torch.bfloat16).to(device=device, dtype=dtype).contiguous()
+        return self.finalize()
+
+    def finalize(self) -> "HybridLM":
+        for blk in self.blocks:
+            blk.mix.finalize()
+        self.dtype, self.device = self.embed.dtype, self.embed.device
+        return self
+
+    def state_tensors(self) -> Dict[str, torch.Tensor]:
+        return {k: v.data for k, v in self.tensor_map().items()}
+
+    def new_pool(self, n_slots: int, max_seq_length: int) -> StatePool:
+        return StatePool(self.config, n_slots, max_seq_length, self.device, self.dtype)
+
+    # ---- the step function ---------------------------------------------------------------------
+    @torch.inference_mode()
+    def hidden(self, tokens: torch.Tensor, plan: H.BatchPlan, pool: StatePool,
+               trace: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+        """Residual stream ``[N, width]`` (fp32) after the last layer for packed int32 ``tokens [N]``."""
+        C, dt = self.config.width, self.dtype
+        for _, n, slot, p0 in plan.seqs:
+            if p0 + n > pool.max_seq_length:
+                raise ValueError(f"sequence of {p0 + n} tokens exceeds the pool's max_seq_length {pool.max_seq_length}")
+        x0 = H.embed_rows(self.embed, tokens)
+        x = x0.clone() if self.loop_in is not None else x0
+        for run, (li, first) in enumerate(self.runs):
+            if first:
+                cat = torch.empty(x.size(0), 2 * C, device=x.device, dtype=dt)
+                H.cast_into(x, cat[:, :C])
+                H.cast_into(x0, cat[:, C:])
+                y = H.linear(cat, self.loop_in)
+                if dt == torch.float32:
+                    x = y
+                else:
+                    H.cast_into(y, x)
+            self.blocks[li](x, plan, pool.runs[run], dt)
+            if trace is not None:
+                trace.append(x.clone())
+        return x
+
+    @torch.inference_mode()
+    def head(self, x: torch.Tensor) -> torch.Tensor:
+        """fp32 logits of residual rows ``x [n, width]``: final norm, tied embedding, soft cap."""
+        h = H.norm_rows(x, self.final_norm.w, self.final_norm.b, self.config.norm_eps, "layer", self.dtype)
+        return H.softcap(H.linear(h, self.embed), self.config.logit_softcap)
+
+    def forward(self, tokens: torch.Tensor, plan: H.BatchPlan, pool: StatePool, rows: Optional[Sequence[int]] = None,
+                trace: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+        x = self.hidden(tokens, plan, pool, trace)
+        if rows is not None:
+            x = x.index_select(0, torch.as_tensor(list(rows), device=x.device, dtype=torch.long))
+        return self.head(x)
+
+
+def load_hybrid(checkpoint_dir: Union[str, Path], device: Union[str, torch.device], dtype: torch.dtype) -> HybridLM:
+    """Build the model a checkpoint folder describes (``config.json`` + ``model.safetensors``) through the registry."""
+    from .registry import architecture_of, model_classes
+
+    d = Path(checkpoint_dir)
+    cfg_cls, model_cls = model_classes(architecture_of(d))
+    cfg = cfg_cls.from_file(d / "config.json")
+    tensors = read_safetensors(d / "model.safetensors")
+    ranks = {k: int(v.shape[0]) for k, v in tensors.items() if k.endswith((".a1", ".g1"))}
+    return model_cls(cfg, ranks).load_tensors(tensors, device, dtype)

@@ -259,3 +259,38 @@ def lookup(name: str) -> Dict[str, Any]:
         if c["hf_config"]["name"] == name:
             return c
     raise ValueError(f"{name!r} is not a supported config name")
+
+
+# ---- architectures whose checkpoints describe themselves (config.json + model.safetensors) ------------------
+# ``config.json["architecture"]`` -> (config class, model class), as dotted paths resolved on first use.
+architectures: Dict[str, Tuple[str, str]] = {
+    "Badapel": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
+}
+
+
+def _resolve(path: str) -> Any:
+    import importlib
+
+    mod, _, attr = path.partition(":")
+    return getattr(importlib.import_module(mod), attr)
+
+
+def architecture_of(checkpoint_dir: Any) -> str:
+    """The ``architecture`` a checkpoint folder declares in ``config.json`` ("" when it has none)."""
+    import json
+    from pathlib import Path
+
+    f = Path(checkpoint_dir) / "config.json"
+    if not f.is_file():
+        return ""
+    with open(f, encoding="utf-8") as fp:
+        return str(json.load(fp).get("architecture", ""))
+
+
+def model_classes(architecture: str) -> Tuple[Any, Any]:
+    """(config class, model class) registered for ``architecture``."""
+    try:
+        cfg_path, model_path = architectures[architecture]
+    except KeyError:
+        raise ValueError(f"{architecture!r} is not a registered architecture (known: {sorted(architectures)})") from None
+    return _resolve(cfg_path), _resolve(model_path)

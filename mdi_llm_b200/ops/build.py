@@ -29,16 +29,59 @@ def nvcc_path() -> Optional[str]:
     return None
 
 
+# The hybrid model family's kernels are a library of their own (``_mdi_hybrid.so``): a checkout that only serves
+# such a model compiles one file, and that file is built with IEEE math (no ``--use_fast_math``) because its
+# 32-bit mode is held to 32-bit rounding.
+HYBRID_LIB = HERE / "_mdi_hybrid.so"
+HYBRID_SOURCES = ("hybrid_mixers.cu",)
+
+
 def sources() -> List[Path]:
-    return sorted(CSRC.glob("*.cu"))
+    return sorted(p for p in CSRC.glob("*.cu") if p.name not in HYBRID_SOURCES)
 
 
 def _digest() -> str:
     h = hashlib.sha256()
-    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [Path(__file__)]):
+    files = [p for p in CSRC.glob("*.cu") if p.name not in HYBRID_SOURCES]
+    for p in sorted(files + list(CSRC.glob("*.cuh")) + [Path(__file__)]):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     return h.hexdigest()
+
+
+def _hybrid_digest() -> str:
+    h = hashlib.sha256()
+    for name in HYBRID_SOURCES:
+        h.update(name.encode())
+        h.update((CSRC / name).read_bytes())
+    return h.hexdigest()
+
+
+def hybrid_is_fresh() -> bool:
+    return HYBRID_LIB.exists() and embedded_digest(HYBRID_LIB) == _hybrid_digest()
+
+
+def build_hybrid(force: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile the hybrid-family kernels into ``_mdi_hybrid.so`` (one nvcc call, IEEE math)."""
+    if not force and hybrid_is_fresh():
+        return HYBRID_LIB
+    nvcc = nvcc_path()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found: cannot build the sm_100a kernels")
+    digest = _hybrid_digest()
+    tmp = HYBRID_LIB.with_suffix(f".{os.getpid()}.tmp.so")
+    cmd = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC", "-shared",
+           f'-DMDI_BUILD_DIGEST_STR="{digest}"', *(["-Xptxas", "-v"] if ptxas_info else []),
+           *[str(CSRC / n) for n in HYBRID_SOURCES], "-o", str(tmp), "-lcudart"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{r.stdout}")
+    if ptxas_info:
+        print(r.stdout)
+    os.replace(tmp, HYBRID_LIB)  # atomic: a concurrent process never loads a half-written library
+    if embedded_digest(HYBRID_LIB) != digest:
+        raise RuntimeError("built library does not carry the source digest")
+    return HYBRID_LIB
 
 
 _MARK = b"MDI_BUILD_DIGEST:"
@@ -109,3 +152,4 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv)
     print(path)
+    print(build_hybrid(force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv))

@@ -1,0 +1,536 @@
+// Kernels of the hybrid (attention + recurrent) model family: packed variable-length batches, slot-indexed state.
+//
+// A step is a packed batch of N tokens from `nseq` sequences.  `meta[4*s] = {first token row, token count, slot,
+// position of the first token}` describes sequence s, `tok_seq[i]` names the sequence of token row i.  The same
+// kernels serve prompts (many tokens per sequence) and decoding (one token per sequence): what differs is only
+// the meta table.  Every kernel is templated on the activation type (bf16 or fp32); sums, norms, softmax, decays
+// and recurrent state are fp32 in both.  This file is compiled WITHOUT fast-math: its exponentials, divisions and
+// square roots are the IEEE ones.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace hyb {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Sum over the block; every thread gets the result.  `red` holds 33 floats.  Safe to call back to back.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float gelu_erff_(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+// ---------------------------------------------------------------------------------------------------------
+// rows: embedding gather, casts, norms, element-wise epilogues
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
+                                  int C) {
+  const T* src = table + (size_t)tokens[blockIdx.x] * C;
+  float* dst = x + (size_t)blockIdx.x * C;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = to_f(src[i]);
+}
+
+template <typename Tin, typename Tout>
+__global__ void cast_rows_kernel(const Tin* __restrict__ in, long long in_stride, Tout* __restrict__ out,
+                                 long long out_stride, int n) {
+  const Tin* src = in + (size_t)blockIdx.x * in_stride;
+  Tout* dst = out + (size_t)blockIdx.x * out_stride;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = from_f<Tout>(to_f(src[i]));
+}
+
+// kind 0: (x - mean) / sqrt(var + eps) * w + b      kind 1: x / sqrt(mean(x^2) + eps) * w
+// accumulate != 0: out (fp32) += result, the residual update of a sandwich block; else out = result.
+template <typename Tin, typename Tw, typename Tout>
+__global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride, const Tw* __restrict__ w,
+                                 const Tw* __restrict__ b, Tout* __restrict__ out, long long out_stride, int n,
+                                 float eps, int kind, int accumulate) {
+  __shared__ float red[33];
+  const Tin* src = in + (size_t)blockIdx.x * in_stride;
+  Tout* dst = out + (size_t)blockIdx.x * out_stride;
+  float mean = 0.f;
+  if (kind == 0) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += to_f(src[i]);
+    mean = block_sum(s, red) / n;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float d = to_f(src[i]) - mean;
+    ss += d * d;
+  }
+  float inv = 1.f / sqrtf(block_sum(ss, red) / n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float y = (to_f(src[i]) - mean) * inv;
+    if (w) y *= to_f(w[i]);
+    if (b) y += to_f(b[i]);
+    if (accumulate) dst[i] = from_f<Tout>(to_f(dst[i]) + y);
+    else dst[i] = from_f<Tout>(y);
+  }
+}
+
+// act 0: gelu(erf) in place.  act 1: out[r, c] = a[r, c] * sigmoid(g[r, c]) where a is stored head-major
+// ([heads, rows, hv]) and out/g are row-major ([rows, heads * hv]).
+template <typename T>
+__global__ void gelu_rows_kernel(T* __restrict__ x, long long total) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = from_f<T>(gelu_erff_(to_f(x[i])));
+}
+template <typename T>
+__global__ void headmajor_gate_kernel(const T* __restrict__ a, const T* __restrict__ g, long long g_stride,
+                                      T* __restrict__ out, int rows, int heads, int hv) {
+  int r = blockIdx.x;
+  int n = heads * hv;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    int h = c / hv, d = c - h * hv;
+    float v = to_f(a[((size_t)h * rows + r) * hv + d]);
+    out[(size_t)r * n + c] = from_f<T>(v * sigmoidf_(to_f(g[(size_t)r * g_stride + c])));
+  }
+}
+template <typename T>
+__global__ void softcap_kernel(const T* __restrict__ in, float* __restrict__ out, long long total, float cap) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) {
+    float v = to_f(in[i]);
+    out[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// latent attention: cache append (norm + rotary) and attention over the shared latent rows
+// ---------------------------------------------------------------------------------------------------------
+// One block per token.  The row `ckv` holds [L latent | R rotary key]: the latent is RMS-normed with `w`, the key
+// part is rotated for the token's position; both go to cache[slot, pos].  The rotary part of each query head
+// (last R of its D + R values) is rotated in place.  Pair (i, i + nrot/2), angle = pos * inv_freq[i].
+template <typename T>
+__global__ void latent_append_kernel(const T* __restrict__ ckv, long long ckv_stride, T* __restrict__ q,
+                                     long long q_stride, const T* __restrict__ w, const float* __restrict__ inv_freq,
+                                     T* __restrict__ cache, long long slot_stride, const int* __restrict__ meta,
+                                     const int* __restrict__ tok_seq, int H, int D, int R, int L, int nrot, float eps) {
+  __shared__ float red[33];
+  int tok = blockIdx.x;
+  const int* m = meta + 4 * tok_seq[tok];
+  int pos = m[3] + tok - m[0];
+  const T* src = ckv + (size_t)tok * ckv_stride;
+  T* dst = cache + (size_t)m[2] * slot_stride + (size_t)pos * (L + R);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < L; i += blockDim.x) {
+    float v = to_f(src[i]);
+    ss += v * v;
+  }
+  float inv = 1.f / sqrtf(block_sum(ss, red) / L + eps);
+  for (int i = threadIdx.x; i < L; i += blockDim.x) dst[i] = from_f<T>(to_f(src[i]) * inv * to_f(w[i]));
+  int half = nrot / 2;
+  // work items: (H + 1) vectors (vector H is the shared key part) x (half pairs, then the R - nrot values that pass);
+  // one thread owns both members of a pair, so the in-place rotation of q needs no barrier
+  int per = half + (R - nrot);
+  for (int idx = threadIdx.x; idx < (H + 1) * per; idx += blockDim.x) {
+    int vec = idx / per, i = idx - vec * per;
+    T* qd = q + (size_t)tok * q_stride + (size_t)vec * (D + R) + D;
+    const T* s = vec < H ? qd : src + L;
+    T* d = vec < H ? qd : dst + L;
+    if (i < half) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      float u = to_f(s[i]), v = to_f(s[i + half]);
+      d[i] = from_f<T>(u * cs - v * sn);
+      d[i + half] = from_f<T>(v * cs + u * sn);
+    } else if (vec == H) {
+      d[nrot + i - half] = s[nrot + i - half];
+    }
+  }
+}
+
+// Attention of H query heads over ONE shared key row per position, whose first Dv entries are also the value
+// (queries arrive already multiplied into the latent space).  Block = one token x 8 heads, one warp per head;
+// a tile of 32 cached rows is staged in shared memory once and used by all 8 heads.  Online softmax in fp32.
+#define LAT_WARPS 8
+#define LAT_TILE 32
+#define LAT_MAXV 16  // Dv <= 512
+template <typename T>
+__global__ void latent_attn_kernel(const T* __restrict__ qlat, const T* __restrict__ q, long long q_stride,
+                                   const T* __restrict__ cache, long long slot_stride, const int* __restrict__ meta,
+                                   const int* __restrict__ tok_seq, T* __restrict__ out, int N, int H, int D, int R,
+                                   int L, float scale) {
+  extern __shared__ float smem[];
+  int Dk = L + R, ldk = Dk + 1;
+  float* sq = smem;                       // [LAT_WARPS][Dk]
+  float* kt = smem + LAT_WARPS * Dk;      // [LAT_TILE][ldk]
+  int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* m = meta + 4 * tok_seq[tok];
+  int nkeys = m[3] + tok - m[0] + 1;
+  int h = blockIdx.y * LAT_WARPS + warp;
+  bool active = h < H;
+  if (active) {
+    for (int d = lane; d < Dk; d += 32) {
+      float v = d < L ? to_f(qlat[((size_t)h * N + tok) * L + d])
+                      : to_f(q[(size_t)tok * q_stride + (size_t)h * (D + R) + D + (d - L)]);
+      sq[warp * Dk + d] = v * scale;
+    }
+  }
+  const T* rows = cache + (size_t)m[2] * slot_stride;
+  float mx = -INFINITY, l = 0.f, acc[LAT_MAXV];
+#pragma unroll
+  for (int i = 0; i < LAT_MAXV; ++i) acc[i] = 0.f;
+  int nv = (L + 31) / 32;
+  for (int t0 = 0; t0 < nkeys; t0 += LAT_TILE) {
+    __syncthreads();
+    int lim = min(LAT_TILE, nkeys - t0);
+    for (int idx = threadIdx.x; idx < lim * Dk; idx += blockDim.x) {
+      int jj = idx / Dk, d = idx - jj * Dk;
+      kt[jj * ldk + d] = to_f(rows[(size_t)(t0 + jj) * Dk + d]);
+    }
+    __syncthreads();
+    if (!active) continue;
+    float s = -INFINITY;
+    if (lane < lim) {
+      s = 0.f;
+      const float* qv = sq + warp * Dk;
+      const float* kv = kt + lane * ldk;
+      for (int d = 0; d < Dk; ++d) s += qv[d] * kv[d];
+    }
+    float mnew = fmaxf(mx, warp_max(s));
+    float corr = expf(mx - mnew);
+    float p = lane < lim ? expf(s - mnew) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < LAT_MAXV; ++i) acc[i] *= corr;
+    for (int jj = 0; jj < lim; ++jj) {
+      float pj = __shfl_sync(0xffffffffu, p, jj);
+      const float* kv = kt + jj * ldk;
+#pragma unroll
+      for (int i = 0; i < LAT_MAXV; ++i)
+        if (i < nv) {
+          int d = lane + 32 * i;
+          if (d < L) acc[i] += pj * kv[d];
+        }
+    }
+    mx = mnew;
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < LAT_MAXV; ++i)
+      if (i < nv) {
+        int d = lane + 32 * i;
+        if (d < L) out[((size_t)h * N + tok) * L + d] = from_f<T>(acc[i] / l);
+      }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// short causal convolution + SiLU over packed sequences, with the last taps-1 inputs kept per slot
+// ---------------------------------------------------------------------------------------------------------
+// y[t, c] = silu(sum_j w[c, j] * x[t - (taps-1-j), c]); inputs before this step come from state[slot]
+// ([taps-1, C], oldest first; zero for a fresh slot).
+template <typename T>
+__global__ void conv_silu_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ w,
+                                 const T* __restrict__ state, T* __restrict__ y, long long y_stride,
+                                 const int* __restrict__ meta, const int* __restrict__ tok_seq, int C, int taps) {
+  int tok = blockIdx.x;
+  const int* m = meta + 4 * tok_seq[tok];
+  int local = tok - m[0];
+  const T* st = state + (size_t)m[2] * (taps - 1) * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      int src = local - (taps - 1 - j);
+      float v = src >= 0 ? to_f(x[(size_t)(m[0] + src) * x_stride + c]) : to_f(st[(size_t)(taps - 1 + src) * C + c]);
+      acc += to_f(w[(size_t)c * taps + j]) * v;
+    }
+    y[(size_t)tok * y_stride + c] = from_f<T>(siluf_(acc));
+  }
+}
+// After the convolution: state[slot] <- the last taps-1 inputs of the sequence (old rows shift up when the step
+// brought fewer than taps-1 tokens).  One thread per channel walks the rows oldest first, so it never reads a row
+// it has already overwritten.
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ x, long long x_stride, T* __restrict__ state,
+                                  const int* __restrict__ meta, int C, int taps) {
+  const int* m = meta + 4 * blockIdx.x;
+  int n = m[1], keep = taps - 1;
+  T* st = state + (size_t)m[2] * keep * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    for (int j = 0; j < keep; ++j) {
+      int src = n - keep + j;  // local index of the input that becomes row j
+      st[(size_t)j * C + c] = src >= 0 ? x[(size_t)(m[0] + src) * x_stride + c] : st[(size_t)(j + n) * C + c];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// gated linear recurrences with a [D, V] state per head (fp32, in shared memory while a step runs)
+// ---------------------------------------------------------------------------------------------------------
+// mode 0 (gated linear attention): a = exp(-softplus(-(z + zb)) / tau);  S = a S + k v^T;  o = S^T (q D^-1/2)
+// mode 1 (gated delta rule):       a = exp(-exp(A_log[h]) softplus(z + zb)); q, k unit vectors (eps 1e-6);
+//                                  S = a S; u = beta (v - S^T k); S += k u^T; o = S^T (q D^-1/2)
+// then o / rms(o) * w * gate, gate = silu(g) (mode 0) or sigmoid(g) (mode 1).
+// Block = one (sequence, head), one thread per value column: columns never interact inside the recurrence.
+struct RecArgs {
+  const void *q, *k, *v, *z, *g, *beta, *zb, *a_log, *w;
+  void* out;
+  float* state;
+  const int* meta;
+  long long q_stride, k_stride, v_stride, z_stride, g_stride, beta_stride, out_stride;
+  int H, G, D, V, mode;
+  float tau, eps;
+};
+
+template <typename T>
+__global__ void gated_recurrence_kernel(RecArgs a) {
+  extern __shared__ float smem[];
+  int D = a.D, V = a.V, h = blockIdx.y, j = threadIdx.x;
+  float* S = smem;            // [D][V]
+  float* sq = S + D * V;      // [D]
+  float* sk = sq + D;
+  float* sa = sk + D;
+  float* red = sa + D;        // [33]
+  const int* m = a.meta + 4 * blockIdx.x;
+  int start = m[0], n = m[1];
+  float* gS = a.state + ((size_t)m[2] * a.H + h) * D * V;
+  for (int i = threadIdx.x; i < D * V; i += blockDim.x) S[i] = gS[i];
+  int kvh = h / (a.H / a.G);
+  const T *q = (const T*)a.q, *k = (const T*)a.k, *v = (const T*)a.v, *z = (const T*)a.z, *g = (const T*)a.g;
+  const T *beta = (const T*)a.beta, *zb = (const T*)a.zb, *w = (const T*)a.w, *alog = (const T*)a.a_log;
+  T* out = (T*)a.out;
+  float rate = a.mode == 1 ? expf(to_f(alog[h])) : 0.f;
+  float dscale = 1.f / sqrtf((float)D);
+  for (int t = 0; t < n; ++t) {
+    size_t row = (size_t)start + t;
+    float pq = 0.f, pk = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      float qv = to_f(q[row * a.q_stride + kvh * D + i]);
+      float kv = to_f(k[row * a.k_stride + kvh * D + i]);
+      float zz = to_f(z[row * a.z_stride + h * D + i]) + (zb ? to_f(zb[h * D + i]) : 0.f);
+      sq[i] = qv;
+      sk[i] = kv;
+      sa[i] = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
+      pq += qv * qv;
+      pk += kv * kv;
+    }
+    float qs = dscale, ks = 1.f;
+    if (a.mode == 1) {
+      float sumq = block_sum(pq, red);
+      float sumk = block_sum(pk, red);
+      qs = dscale / sqrtf(sumq + 1e-6f);
+      ks = 1.f / sqrtf(sumk + 1e-6f);
+    } else {
+      __syncthreads();
+    }
+    float o = 0.f;
+    if (j < V) {
+      float u = to_f(v[row * a.v_stride + h * V + j]);
+      if (a.mode == 1) {
+        float r = 0.f;
+        for (int i = 0; i < D; ++i) r += sa[i] * S[i * V + j] * (sk[i] * ks);
+        u = sigmoidf_(to_f(beta[row * a.beta_stride + h])) * (u - r);
+      }
+      for (int i = 0; i < D; ++i) {
+        float s = sa[i] * S[i * V + j] + (sk[i] * ks) * u;
+        S[i * V + j] = s;
+        o += s * (sq[i] * qs);
+      }
+    }
+    float ss = block_sum(j < V ? o * o : 0.f, red);
+    if (j < V) {
+      float y = o / sqrtf(ss / V + a.eps) * to_f(w[j]);
+      float gv = to_f(g[row * a.g_stride + h * V + j]);
+      y *= a.mode == 1 ? sigmoidf_(gv) : siluf_(gv);
+      out[row * a.out_stride + h * V + j] = from_f<T>(y);
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < D * V; i += blockDim.x) gS[i] = S[i];
+}
+
+}  // namespace hyb
+
+using namespace hyb;
+
+#define HYB_DISPATCH(dt, expr_bf16, expr_f32) \
+  do {                                        \
+    if ((dt) == 0) { expr_bf16; } else { expr_f32; } \
+  } while (0)
+
+extern "C" {
+
+// dtype codes: 0 = bf16, 1 = fp32
+int hyb_embed_rows(const void* table, const int* tokens, float* x, int N, int C, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  HYB_DISPATCH(dt, (embed_rows_kernel<bf16><<<N, 256, 0, st>>>((const bf16*)table, tokens, x, C)),
+               (embed_rows_kernel<float><<<N, 256, 0, st>>>((const float*)table, tokens, x, C)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_cast_rows(const void* in, long long in_stride, int in_dt, void* out, long long out_stride, int out_dt, int rows,
+                  int n, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (in_dt == 1 && out_dt == 0)
+    cast_rows_kernel<float, bf16><<<rows, 256, 0, st>>>((const float*)in, in_stride, (bf16*)out, out_stride, n);
+  else if (in_dt == 1 && out_dt == 1)
+    cast_rows_kernel<float, float><<<rows, 256, 0, st>>>((const float*)in, in_stride, (float*)out, out_stride, n);
+  else if (in_dt == 0 && out_dt == 1)
+    cast_rows_kernel<bf16, float><<<rows, 256, 0, st>>>((const bf16*)in, in_stride, (float*)out, out_stride, n);
+  else
+    cast_rows_kernel<bf16, bf16><<<rows, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, out_stride, n);
+  return (int)cudaGetLastError();
+}
+
+// w/b have dtype w_dt; in has in_dt; out has out_dt.  Supported (in, w, out): all fp32, or w bf16 with in/out in
+// {bf16, fp32}.
+int hyb_norm_rows(const void* in, long long in_stride, int in_dt, const void* w, const void* b, int w_dt, void* out,
+                  long long out_stride, int out_dt, int rows, int n, float eps, int kind, int accumulate,
+                  cudaStream_t st) {
+  if (rows == 0) return 0;
+#define NR(TI, TW, TO)                                                                                              \
+  norm_rows_kernel<TI, TW, TO><<<rows, 256, 0, st>>>((const TI*)in, in_stride, (const TW*)w, (const TW*)b, (TO*)out, \
+                                                      out_stride, n, eps, kind, accumulate)
+  if (w_dt == 1) {
+    if (in_dt != 1 || out_dt != 1) return -3;
+    NR(float, float, float);
+  } else if (in_dt == 1 && out_dt == 0) NR(float, bf16, bf16);
+  else if (in_dt == 0 && out_dt == 1) NR(bf16, bf16, float);
+  else if (in_dt == 0 && out_dt == 0) NR(bf16, bf16, bf16);
+  else NR(float, bf16, float);
+#undef NR
+  return (int)cudaGetLastError();
+}
+
+int hyb_gelu_rows(void* x, long long total, int dt, cudaStream_t st) {
+  if (total == 0) return 0;
+  int blocks = (int)((total + 255) / 256);
+  HYB_DISPATCH(dt, (gelu_rows_kernel<bf16><<<blocks, 256, 0, st>>>((bf16*)x, total)),
+               (gelu_rows_kernel<float><<<blocks, 256, 0, st>>>((float*)x, total)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_headmajor_gate(const void* a, const void* g, long long g_stride, void* out, int rows, int heads, int hv, int dt,
+                       cudaStream_t st) {
+  if (rows == 0) return 0;
+  HYB_DISPATCH(dt,
+               (headmajor_gate_kernel<bf16><<<rows, 256, 0, st>>>((const bf16*)a, (const bf16*)g, g_stride, (bf16*)out,
+                                                                  rows, heads, hv)),
+               (headmajor_gate_kernel<float><<<rows, 256, 0, st>>>((const float*)a, (const float*)g, g_stride,
+                                                                   (float*)out, rows, heads, hv)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_softcap(const void* in, float* out, long long total, float cap, int dt, cudaStream_t st) {
+  if (total == 0) return 0;
+  int blocks = (int)((total + 255) / 256);
+  HYB_DISPATCH(dt, (softcap_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, out, total, cap)),
+               (softcap_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, out, total, cap)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_latent_append(const void* ckv, long long ckv_stride, void* q, long long q_stride, const void* w,
+                      const float* inv_freq, void* cache, long long slot_stride, const int* meta, const int* tok_seq,
+                      int N, int H, int D, int R, int L, int nrot, float eps, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  if (nrot > R || (nrot & 1)) return -2;
+  int threads = 256;
+  HYB_DISPATCH(dt,
+               (latent_append_kernel<bf16><<<N, threads, 0, st>>>((const bf16*)ckv, ckv_stride, (bf16*)q, q_stride,
+                                                                  (const bf16*)w, inv_freq, (bf16*)cache, slot_stride,
+                                                                  meta, tok_seq, H, D, R, L, nrot, eps)),
+               (latent_append_kernel<float><<<N, threads, 0, st>>>((const float*)ckv, ckv_stride, (float*)q, q_stride,
+                                                                   (const float*)w, inv_freq, (float*)cache,
+                                                                   slot_stride, meta, tok_seq, H, D, R, L, nrot, eps)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const void* cache, long long slot_stride,
+                    const int* meta, const int* tok_seq, void* out, int N, int H, int D, int R, int L, float scale,
+                    int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  if (L > 32 * LAT_MAXV) return -3;
+  int Dk = L + R;
+  size_t smem = (size_t)(LAT_WARPS * Dk + LAT_TILE * (Dk + 1)) * sizeof(float);
+  if (smem > 200 * 1024) return -3;
+  dim3 grid(N, (H + LAT_WARPS - 1) / LAT_WARPS);
+  if (dt == 0) {
+    cudaFuncSetAttribute(latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    latent_attn_kernel<bf16><<<grid, LAT_WARPS * 32, smem, st>>>((const bf16*)qlat, (const bf16*)q, q_stride,
+                                                                 (const bf16*)cache, slot_stride, meta, tok_seq,
+                                                                 (bf16*)out, N, H, D, R, L, scale);
+  } else {
+    cudaFuncSetAttribute(latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    latent_attn_kernel<float><<<grid, LAT_WARPS * 32, smem, st>>>((const float*)qlat, (const float*)q, q_stride,
+                                                                  (const float*)cache, slot_stride, meta, tok_seq,
+                                                                  (float*)out, N, H, D, R, L, scale);
+  }
+  return (int)cudaGetLastError();
+}
+
+int hyb_conv_silu(const void* x, long long x_stride, const void* w, void* state, void* y, long long y_stride,
+                  const int* meta, const int* tok_seq, int N, int nseq, int C, int taps, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  dim3 grid(N, (C + 255) / 256), sgrid(nseq, (C + 255) / 256);
+  if (dt == 0) {
+    conv_silu_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, x_stride, (const bf16*)w, (const bf16*)state,
+                                                 (bf16*)y, y_stride, meta, tok_seq, C, taps);
+    if (taps > 1) conv_state_kernel<bf16><<<sgrid, 256, 0, st>>>((const bf16*)x, x_stride, (bf16*)state, meta, C, taps);
+  } else {
+    conv_silu_kernel<float><<<grid, 256, 0, st>>>((const float*)x, x_stride, (const float*)w, (const float*)state,
+                                                  (float*)y, y_stride, meta, tok_seq, C, taps);
+    if (taps > 1) conv_state_kernel<float><<<sgrid, 256, 0, st>>>((const float*)x, x_stride, (float*)state, meta, C, taps);
+  }
+  return (int)cudaGetLastError();
+}
+
+int hyb_gated_recurrence(const RecArgs* args, int nseq, int dt, cudaStream_t st) {
+  if (nseq == 0) return 0;
+  RecArgs a = *args;
+  if (a.V > 1024 || a.H % a.G) return -3;
+  size_t smem = ((size_t)a.D * a.V + 3 * a.D + 33) * sizeof(float);
+  if (smem > 220 * 1024) return -3;
+  int threads = (a.V + 31) / 32 * 32;
+  dim3 grid(nseq, a.H);
+  if (dt == 0) {
+    cudaFuncSetAttribute(gated_recurrence_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gated_recurrence_kernel<bf16><<<grid, threads, smem, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(gated_recurrence_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gated_recurrence_kernel<float><<<grid, threads, smem, st>>>(a);
+  }
+  return (int)cudaGetLastError();
+}
+
+#ifndef MDI_BUILD_DIGEST_STR
+#define MDI_BUILD_DIGEST_STR "unknown"
+#endif
+const char* hyb_build_digest() { return "MDI_BUILD_DIGEST:" MDI_BUILD_DIGEST_STR; }
+
+const char* hyb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
+
+}  // extern "C"

@@ -1,0 +1,386 @@
+"""Operations of the hybrid (attention + recurrent) model family over packed variable-length batches.
+
+Every function has two bodies.  On a CUDA tensor it launches the sm_100a kernel of ``csrc/hybrid_mixers.cu``
+(library ``_mdi_hybrid.so``, built on first use; a missing or unbuildable library raises — a CUDA tensor never
+takes the PyTorch body).  On a CPU tensor it runs the same arithmetic with plain PyTorch operations, which is how
+the models are brought up and tested on a machine without a GPU.
+
+A *plan* (:class:`BatchPlan`) describes the step: for each sequence its first row in the packed token matrix, its
+token count, its state slot and the position of its first token.  Prompts and one-token decoding differ only in
+the plan.  Row-wise inputs may be column slices of a wider matrix (one fused projection feeds several
+consumers): the functions pass the row stride down, the last dimension must be dense.
+
+What is always computed in fp32, whatever the activation type: normalisation statistics, softmax, decays and
+their logarithms, gates of the recurrences, unit norms, the recurrent state itself and the residual stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import build as _build
+
+__all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
+           "headmajor_gate", "softcap", "latent_append", "latent_attn", "conv_silu", "gated_recurrence", "linear",
+           "rotary_inv_freq"]
+
+
+class HybridOpsError(RuntimeError):
+    pass
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class _RecArgs(ctypes.Structure):
+    _fields_ = ([(n, c_void_p) for n in ("q", "k", "v", "z", "g", "beta", "zb", "a_log", "w", "out", "state", "meta")]
+                + [(n, c_longlong) for n in ("q_stride", "k_stride", "v_stride", "z_stride", "g_stride", "beta_stride",
+                                             "out_stride")]
+                + [(n, c_int) for n in ("H", "G", "D", "V", "mode")] + [("tau", c_float), ("eps", c_float)])
+
+
+def lib() -> ctypes.CDLL:
+    """Load ``_mdi_hybrid.so``, compiling it first when it is missing or older than its source."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _build.hybrid_is_fresh():
+        if _build.nvcc_path() is None:
+            raise HybridOpsError("the hybrid kernel library is not built and nvcc is not available")
+        _build.build_hybrid()
+    h = ctypes.CDLL(str(_build.HYBRID_LIB))
+    vp, i32, i64, f32 = c_void_p, c_int, c_longlong, c_float
+    h.hyb_error_string.restype = ctypes.c_char_p
+    h.hyb_error_string.argtypes = [i32]
+    h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    h.hyb_cast_rows.argtypes = [vp, i64, i32, vp, i64, i32, i32, i32, vp]
+    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, vp]
+    h.hyb_gelu_rows.argtypes = [vp, i64, i32, vp]
+    h.hyb_headmajor_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
+    h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
+    h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
+    h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
+    h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
+    h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, vp]
+    _lib = h
+    return h
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        msg = {-2: "invalid shape/alignment", -3: "unsupported configuration"}.get(code) or lib().hyb_error_string(code).decode()
+        raise HybridOpsError(f"{what} failed: {msg} ({code})")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise HybridOpsError(f"unsupported dtype {t.dtype}")
+
+
+def _st() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _rows(t: torch.Tensor) -> Tuple[int, int]:
+    """(row stride, width) of a 2-D tensor or column slice whose last dimension is dense."""
+    if t.dim() != 2 or (t.size(1) > 1 and t.stride(1) != 1):
+        raise HybridOpsError(f"expected rows with a dense last dimension, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0), t.size(1)
+
+
+@dataclass
+class BatchPlan:
+    """One step's packed batch: ``seqs[i] = (first row, tokens, slot, position of the first token)``."""
+
+    seqs: List[Tuple[int, int, int, int]]
+    n_tokens: int
+    meta: torch.Tensor      # int32 [n_seq, 4] on the compute device
+    tok_seq: torch.Tensor   # int32 [n_tokens]: sequence index of every row
+    positions: torch.Tensor  # int64 [n_tokens]
+
+    @classmethod
+    def make(cls, lengths: Sequence[int], slots: Sequence[int], starts: Sequence[int], device: torch.device) -> "BatchPlan":
+        seqs, row = [], 0
+        for n, s, p in zip(lengths, slots, starts):
+            seqs.append((row, int(n), int(s), int(p)))
+            row += int(n)
+        meta = torch.tensor(seqs, dtype=torch.int32).view(-1, 4)
+        tok_seq = torch.repeat_interleave(torch.arange(len(seqs), dtype=torch.int32), meta[:, 1].long())
+        pos = torch.cat([torch.arange(p, p + n) for _, n, _, p in seqs]) if seqs else torch.zeros(0, dtype=torch.long)
+        return cls(seqs, row, meta.to(device), tok_seq.to(device), pos.to(device))
+
+    @property
+    def last_rows(self) -> List[int]:
+        return [r + n - 1 for r, n, _, _ in self.seqs]
+
+
+def rotary_inv_freq(dims: int, base: float, device: torch.device) -> torch.Tensor:
+    """``base^(-2i/dims)`` for ``i < dims/2``, evaluated in float64 and rounded once to fp32."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return (float(base) ** (-2.0 * i / dims)).to(torch.float32).to(device)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# matrix products (vendor GEMM on both devices; fp32 means fp32: TF32 is switched off for the call)
+# ---------------------------------------------------------------------------------------------------------
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` in the activation type with fp32 accumulation."""
+    if x.is_cuda and x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise HybridOpsError("TF32 matrix products are on; fp32 mode needs torch.backends.cuda.matmul.allow_tf32 = False")
+    return F.linear(x, w)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# rows
+# ---------------------------------------------------------------------------------------------------------
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """fp32 rows of ``table`` for int32 ``tokens [N]``."""
+    if not table.is_cuda:
+        return table[tokens.long()].float()
+    x = torch.empty(tokens.numel(), table.size(1), device=table.device, dtype=torch.float32)
+    _check(lib().hyb_embed_rows(table.data_ptr(), tokens.data_ptr(), x.data_ptr(), tokens.numel(), table.size(1),
+                                _dt(table), _st()), "embed_rows")
+    return x
+
+
+def cast_into(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """``dst[:] = src`` with a type change; both may be column slices."""
+    if not src.is_cuda:
+        dst.copy_(src)
+        return
+    ss, n = _rows(src)
+    ds, n2 = _rows(dst)
+    assert n == n2 and src.size(0) == dst.size(0)
+    _check(lib().hyb_cast_rows(src.data_ptr(), ss, _dt(src), dst.data_ptr(), ds, _dt(dst), src.size(0), n, _st()), "cast_rows")
+
+
+def _norm_torch(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, kind: str) -> torch.Tensor:
+    xf = x.float()
+    if kind == "layer":
+        xf = xf - xf.mean(-1, keepdim=True)
+    y = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
+    if w is not None:
+        y = y * w.float()
+    if b is not None:
+        y = y + b.float()
+    return y
+
+
+def norm_rows(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, kind: str,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """Layer norm (``kind="layer"``: weight and bias) or RMS norm (``kind="rms"``) of every row, statistics in fp32."""
+    if not x.is_cuda:
+        return _norm_torch(x, w, b, eps, kind).to(out_dtype)
+    xs, n = _rows(x)
+    out = torch.empty(x.size(0), n, device=x.device, dtype=out_dtype)
+    ref = w if w is not None else x
+    _check(lib().hyb_norm_rows(x.data_ptr(), xs, _dt(x), None if w is None else w.data_ptr(),
+                               None if b is None else b.data_ptr(), _dt(ref), out.data_ptr(), n, _dt(out), x.size(0), n,
+                               eps, 0 if kind == "layer" else 1, 0, _st()), "norm_rows")
+    return out
+
+
+def norm_accumulate(resid: torch.Tensor, y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float,
+                    kind: str = "layer") -> None:
+    """``resid += norm(y)``: the post-norm and the residual sum of a sandwich block in one pass (fp32 residual)."""
+    if resid.dtype != torch.float32:
+        raise HybridOpsError("the residual stream is fp32")
+    if not y.is_cuda:
+        resid.add_(_norm_torch(y, w, b, eps, kind))
+        return
+    ys, n = _rows(y)
+    _check(lib().hyb_norm_rows(y.data_ptr(), ys, _dt(y), w.data_ptr(), None if b is None else b.data_ptr(), _dt(w),
+                               resid.data_ptr(), resid.stride(0), 1, y.size(0), n, eps, 0 if kind == "layer" else 1, 1,
+                               _st()), "norm_accumulate")
+
+
+def gelu_(x: torch.Tensor) -> torch.Tensor:
+    """Exact (erf) GELU in place on a dense tensor."""
+    if not x.is_cuda:
+        return x.copy_(F.gelu(x.float()).to(x.dtype))
+    assert x.is_contiguous()
+    _check(lib().hyb_gelu_rows(x.data_ptr(), x.numel(), _dt(x), _st()), "gelu")
+    return x
+
+
+def headmajor_gate(a: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """``a [heads, rows, hv]`` (head-major) times ``sigmoid(g [rows, heads*hv])`` -> ``[rows, heads*hv]``."""
+    H, N, hv = a.shape
+    if not a.is_cuda:
+        return (a.permute(1, 0, 2).reshape(N, H * hv).float() * torch.sigmoid(g.float())).to(a.dtype)
+    assert a.is_contiguous()
+    gs, _ = _rows(g)
+    out = torch.empty(N, H * hv, device=a.device, dtype=a.dtype)
+    _check(lib().hyb_headmajor_gate(a.data_ptr(), g.data_ptr(), gs, out.data_ptr(), N, H, hv, _dt(a), _st()), "headmajor_gate")
+    return out
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """fp32 ``cap * tanh(logits / cap)`` (``cap <= 0``: a plain conversion to fp32)."""
+    if not logits.is_cuda:
+        lf = logits.float()
+        return cap * torch.tanh(lf / cap) if cap > 0 else lf
+    assert logits.is_contiguous()
+    out = torch.empty(logits.shape, device=logits.device, dtype=torch.float32)
+    _check(lib().hyb_softcap(logits.data_ptr(), out.data_ptr(), logits.numel(), float(cap), _dt(logits), _st()), "softcap")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# latent attention
+# ---------------------------------------------------------------------------------------------------------
+def latent_append(ckv: torch.Tensor, q: torch.Tensor, w: torch.Tensor, inv_freq: torch.Tensor, cache: torch.Tensor,
+                  plan: BatchPlan, H: int, D: int, R: int, L: int, nrot: int, eps: float) -> None:
+    """Per token: RMS-norm the latent (first ``L`` of the ``ckv`` row), rotate the shared key part (last ``R``) and
+    write both to ``cache[slot, pos]``; rotate the last ``R`` values of each of the ``H`` query heads of ``q`` in
+    place.  Rotation pairs entry ``i`` with ``i + nrot/2`` for the first ``nrot`` entries, angle ``pos * inv_freq[i]``."""
+    if not ckv.is_cuda:
+        N = ckv.size(0)
+        pos = plan.positions.float()
+        ang = pos[:, None] * inv_freq[None, :]
+        cs, sn = torch.cos(ang), torch.sin(ang)
+        half = nrot // 2
+
+        def rot(x: torch.Tensor) -> torch.Tensor:  # [..., R] with a leading token axis
+            xf = x.float()
+            u, v = xf[..., :half], xf[..., half:nrot]
+            c, s = (cs, sn) if xf.dim() == 2 else (cs[:, None, :], sn[:, None, :])
+            return torch.cat((u * c - v * s, v * c + u * s, xf[..., nrot:]), -1).to(x.dtype)
+
+        lat = _norm_torch(ckv[:, :L], w, None, eps, "rms").to(cache.dtype)
+        kr = rot(ckv[:, L:])
+        qv = q.view(N, H, D + R)
+        qv[..., D:] = rot(qv[..., D:])
+        for r0, n, slot, p0 in plan.seqs:
+            cache[slot, p0:p0 + n, :L] = lat[r0:r0 + n]
+            cache[slot, p0:p0 + n, L:] = kr[r0:r0 + n]
+        return
+    cs_, _ = _rows(ckv)
+    qs, _ = _rows(q)
+    _check(lib().hyb_latent_append(ckv.data_ptr(), cs_, q.data_ptr(), qs, w.data_ptr(), inv_freq.data_ptr(), cache.data_ptr(),
+                                   cache.stride(0), plan.meta.data_ptr(), plan.tok_seq.data_ptr(), ckv.size(0), H, D, R, L,
+                                   nrot, eps, _dt(ckv), _st()), "latent_append")
+
+
+def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: BatchPlan, H: int, D: int, R: int, L: int,
+                scale: float) -> torch.Tensor:
+    """Causal softmax attention of ``H`` heads over the cached rows ``[L latent | R rotated key]`` of each token's slot.
+    The query of head ``h`` is ``[qlat[h, tok] | q[tok, h, D:]]``, the value of a row is its latent part.
+    Returns the attended latents ``[H, N, L]``."""
+    N = q.size(0)
+    if not q.is_cuda:
+        out = torch.empty(H, N, L, dtype=q.dtype)
+        qr = q.view(N, H, D + R)[..., D:].permute(1, 0, 2)
+        qq = torch.cat((qlat, qr), -1).float() * scale  # [H, N, L+R]
+        for r0, n, slot, p0 in plan.seqs:
+            rows = cache[slot, :p0 + n].float()
+            s = qq[:, r0:r0 + n] @ rows.T  # [H, n, keys]
+            keys = torch.arange(p0 + n)
+            s = s.masked_fill(keys[None, None, :] > (p0 + torch.arange(n))[None, :, None], float("-inf"))
+            out[:, r0:r0 + n] = (torch.softmax(s, -1) @ rows[:, :L]).to(q.dtype)
+        return out
+    assert qlat.is_contiguous()
+    qs, _ = _rows(q)
+    out = torch.empty(H, N, L, device=q.device, dtype=q.dtype)
+    _check(lib().hyb_latent_attn(qlat.data_ptr(), q.data_ptr(), qs, cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
+                                 plan.tok_seq.data_ptr(), out.data_ptr(), N, H, D, R, L, float(scale), _dt(q), _st()),
+           "latent_attn")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# short convolution and the gated recurrences
+# ---------------------------------------------------------------------------------------------------------
+def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, plan: BatchPlan) -> torch.Tensor:
+    """Causal per-channel convolution over time (``w [C, taps]``, last column = current token) then SiLU.
+    ``state [slots, taps-1, C]`` supplies the inputs before this step and is updated to the step's last ones."""
+    C, taps = w.shape
+    if not x.is_cuda:
+        y = torch.empty(x.size(0), C, dtype=x.dtype)
+        for r0, n, slot, _ in plan.seqs:
+            full = torch.cat((state[slot], x[r0:r0 + n]), 0).float()  # [taps-1+n, C]
+            acc = torch.zeros(n, C)
+            for j in range(taps):
+                acc += full[j:j + n] * w[:, j].float()
+            y[r0:r0 + n] = F.silu(acc).to(x.dtype)
+            if taps > 1:
+                state[slot] = full[-(taps - 1):].to(state.dtype)
+        return y
+    xs, _ = _rows(x)
+    y = torch.empty(x.size(0), C, device=x.device, dtype=x.dtype)
+    _check(lib().hyb_conv_silu(x.data_ptr(), xs, w.data_ptr(), state.data_ptr(), y.data_ptr(), C, plan.meta.data_ptr(),
+                               plan.tok_seq.data_ptr(), x.size(0), len(plan.seqs), C, taps, _dt(x), _st()), "conv_silu")
+    return y
+
+
+def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, g: torch.Tensor,
+                     w: torch.Tensor, state: torch.Tensor, plan: BatchPlan, *, heads: int, kv_heads: int, dim: int,
+                     vdim: int, mode: str, eps: float, zb: Optional[torch.Tensor] = None, tau: float = 1.0,
+                     beta: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A linear recurrence with a ``[dim, vdim]`` fp32 state per head and slot, read out, normed and gated.
+
+    ``mode="gla"``:   ``a = sigmoid(z + zb)^(1/tau)``; ``S = diag(a) S + k v^T``; ``o = S^T q / sqrt(dim)``; gate SiLU.
+    ``mode="delta"``: ``a = exp(-exp(a_log) softplus(z + zb))``; q, k made unit vectors (eps 1e-6);
+    ``S = diag(a) S``; ``u = sigmoid(beta) (v - S^T k)``; ``S += k u^T``; ``o = S^T q / sqrt(dim)``; gate sigmoid.
+    Output per head: ``o / rms(o) * w * gate(g)``, rows ``[N, heads * vdim]``.  ``state [slots, heads, dim, vdim]``
+    is read at the start of the step and written back at its end.
+    """
+    N = v.size(0)
+    H, G, D, V = heads, kv_heads, dim, vdim
+    if not q.is_cuda:
+        out = torch.empty(N, H * V, dtype=v.dtype)
+        rep = H // G
+        zf = z.float().view(N, H, D) + (zb.float().view(H, D) if zb is not None else 0.0)
+        if mode == "delta":
+            a = torch.exp(-torch.exp(a_log.float())[None, :, None] * F.softplus(zf))
+            bt = torch.sigmoid(beta.float())
+        else:
+            a = torch.exp(F.logsigmoid(zf) / tau)
+        qf = q.float().reshape(N, G, D).repeat_interleave(rep, 1)
+        kf = k.float().reshape(N, G, D).repeat_interleave(rep, 1)
+        if mode == "delta":
+            qf = qf / torch.sqrt((qf * qf).sum(-1, keepdim=True) + 1e-6)
+            kf = kf / torch.sqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+        qf = qf * D ** -0.5
+        vf = v.float().reshape(N, H, V)
+        gf = g.float().reshape(N, H, V)
+        gate = torch.sigmoid(gf) if mode == "delta" else F.silu(gf)
+        for r0, n, slot, _ in plan.seqs:
+            S = state[slot].clone()  # [H, D, V]
+            for t in range(r0, r0 + n):
+                S = a[t][:, :, None] * S
+                u = vf[t]
+                if mode == "delta":
+                    u = bt[t][:, None] * (u - torch.einsum("hdv,hd->hv", S, kf[t]))
+                S = S + kf[t][:, :, None] * u[:, None, :]
+                o = torch.einsum("hdv,hd->hv", S, qf[t])
+                o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * w.float()
+                out[t] = (o * gate[t]).reshape(-1).to(v.dtype)
+            state[slot] = S
+        return out
+    if state.dtype != torch.float32:
+        raise HybridOpsError("recurrent state is fp32")
+    out = torch.empty(N, H * V, device=v.device, dtype=v.dtype)
+    a = _RecArgs()
+    a.q, a.k, a.v, a.z, a.g = q.data_ptr(), k.data_ptr(), v.data_ptr(), z.data_ptr(), g.data_ptr()
+    a.beta = None if beta is None else beta.data_ptr()
+    a.zb = None if zb is None else zb.data_ptr()
+    a.a_log = None if a_log is None else a_log.data_ptr()
+    a.w, a.out, a.state, a.meta = w.data_ptr(), out.data_ptr(), state.data_ptr(), plan.meta.data_ptr()
+    a.q_stride, a.k_stride, a.v_stride = _rows(q)[0], _rows(k)[0], _rows(v)[0]
+    a.z_stride, a.g_stride = _rows(z)[0], _rows(g)[0]
+    a.beta_stride = 0 if beta is None else _rows(beta)[0]
+    a.out_stride = H * V
+    a.H, a.G, a.D, a.V, a.mode = H, G, D, V, 1 if mode == "delta" else 0
+    a.tau, a.eps = float(tau), float(eps)
+    _check(lib().hyb_gated_recurrence(ctypes.byref(a), len(plan.seqs), _dt(v), _st()), "gated_recurrence")
+    return out
