@@ -40,7 +40,54 @@ def build_parser() -> argparse.ArgumentParser:
     return p
 
 
+def run_hybrid(args) -> int:
+    """Checkpoints that describe themselves (``config.json`` with an ``architecture`` + ``model.safetensors``): the
+    samples are generated together by the hybrid runner's batch scheduler.  Prompts are byte-level token ids folded
+    into the vocabulary when the folder has no tokenizer."""
+    import torch
+
+    from .. import config as C
+    from ..models.hybrid import load_hybrid
+    from ..parallel.hybrid_runner import HybridRunner
+    from ..parallel.scheduler import SamplingParams
+
+    seed_everything(args.seed)
+    device = args.device or C.default_device()
+    dtype = C.DTYPE_TORCH_MAPPING[args.dtype or ("bfloat16" if "cuda" in device else "float32")]
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model = load_hybrid(args.ckpt, device, dtype)
+    vocab = model.config.vocab
+    try:
+        from ..text.tokenizer import Tokenizer
+
+        tok = Tokenizer(args.ckpt)
+        prompts = [tok.encode(args.prompt).tolist() for _ in range(args.n_samples)]
+        decode = lambda ids: tok.decode(torch.tensor(ids))  # noqa: E731
+    except (NotImplementedError, FileNotFoundError):
+        prompts = [[b % vocab for b in args.prompt.encode()] or [0] for _ in range(args.n_samples)]
+        decode = lambda ids: " ".join(map(str, ids))  # noqa: E731
+    greedy = args.greedy
+    sampling = SamplingParams.greedy() if greedy else SamplingParams(
+        temperature=args.temperature if args.temperature is not None else C.TEMPERATURE,
+        top_k=min(args.top_k if args.top_k is not None else C.TOP_K, vocab), seed=args.seed)
+    seq_len = args.sequence_length or (max(map(len, prompts)) + args.n_tokens)
+    runner = HybridRunner(model, seq_len, n_slots=len(prompts))
+    t0 = time.time()
+    outs = runner.generate(prompts, args.n_tokens, sampling)
+    total = time.time() - t0
+    for i, (p, out) in enumerate(zip(prompts, outs)):
+        print("-------------------------------------------------")
+        print(f"Sample {i + 1}:\n{decode(out[len(p):])}\n")
+    n_gen = sum(len(o) - len(p) for o, p in zip(outs, prompts))
+    print(f"Total generation time: {total:.3f} s ({n_gen / total:.1f} tokens/s, engine: hybrid/{device})")
+    return 0
+
+
 def run(args) -> int:
+    from ..models.registry import architecture_of
+
+    if architecture_of(args.ckpt):
+        return run_hybrid(args)
     import torch
 
     from .. import config as C

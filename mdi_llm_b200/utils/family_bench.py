@@ -1,0 +1,236 @@
+"""Throughput of the hybrid family beside the closest transformer of the same size (``bench.py --family hybrid``).
+
+For each width a 4-layer hybrid model (latent attention, gated delta rule, gated linear attention, latent attention;
+dense erf-GELU feed-forward of 4x width) and a 4-layer Llama-style transformer of the same width (GQA, gated MLP
+sized to the same parameter count) are built with random weights.  Measured with CUDA events after warm-up:
+
+* prefill: one prompt of ``prompt_len`` tokens, tokens/s;
+* decode: one token per step at a context of ``prompt_len`` tokens, tokens/s, for one stream (what the transformer
+  engine's recurrent pipeline runs per stage) and for a batch of streams (hybrid only: its runner batches);
+* the hybrid family's own kernels one by one on the prefill shapes and on the decode shapes, with achieved bytes/s
+  and FLOP/s against the measured peaks, beside the transformer's attention kernels on the same token counts.
+
+An L2 flush (a write larger than L2) separates timed iterations of the single-kernel measurements.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Callable, Dict, List
+
+import torch
+
+__all__ = ["run_family_compare", "hybrid_bench_config"]
+
+
+def hybrid_bench_config(width: int) -> Dict[str, Any]:
+    h = width // 128
+    lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 4 * width},
+           "mixer": {"heads": h, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": min(1536, width),
+                     "scale": 192 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}}
+    delta = {"type": "channel_delta", "mlp": {"kind": "dense", "ff": 4 * width},
+             "mixer": {"heads": h, "kv_heads": max(1, h // 2), "dim": 128, "vdim": 128, "conv": 4}}
+    gla = {"type": "gla", "mlp": {"kind": "dense", "ff": 4 * width}, "mixer": {"heads": h, "dim": 64, "vdim": 128, "tau": 16.0}}
+    return {"architecture": "Badapel", "vocab": 32000, "width": width, "layers": [lat, delta, gla, dict(lat)],
+            "norm": {"eps": 1e-6}, "logit_softcap": 30.0}
+
+
+def _time(fn: Callable[[], Any], iters: int, warmup: int, flush: Any = None) -> float:
+    """Median milliseconds of ``fn`` over ``iters`` runs (CUDA events; optional L2 flush between runs)."""
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _peaks() -> Dict[str, float]:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as fp:
+            d = json.load(fp)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int) -> Dict[str, Any]:
+    from ..models.config import HybridConfig
+    from ..models.hybrid import HybridLM
+    from ..parallel.hybrid_runner import HybridRunner
+
+    dev = torch.device("cuda")
+    cfg = HybridConfig.from_dict(hybrid_bench_config(width))
+    model = HybridLM(cfg, {}).init_random(dev, torch.bfloat16, seed=1)
+    params = sum(p.numel() for p in model.tensor_map().values())
+    out: Dict[str, Any] = {"params_m": round(params / 1e6, 1)}
+    prompt = torch.randint(0, cfg.vocab, (prompt_len,)).tolist()
+    S = prompt_len + steps + warmup + 8
+
+    def prefill_once() -> None:
+        r = HybridRunner(model, S, n_slots=1, use_graphs=False)
+        prefill_once.r = r
+        r.step([("p", prompt)])
+
+    # the runner is rebuilt per run (a pool of zeros): its allocation is outside what a serving loop pays per
+    # prompt, so time only the step by pre-building
+    runners = [HybridRunner(model, S, n_slots=1, use_graphs=False) for _ in range(warmup + 5)]
+    it = iter(runners)
+    ms = _time(lambda: next(it).step([("p", prompt)]), 5, warmup)
+    out["prefill_tok_s"] = round(prompt_len / ms * 1e3, 1)
+    out["prefill_ms"] = round(ms, 3)
+    del runners
+    for b in (1, batch):
+        r = HybridRunner(model, S, n_slots=b)
+        r.step([(i, prompt) for i in range(b)])
+        tok = [(i, [1]) for i in range(b)]
+        ms = _time(lambda: r.step(tok), steps, warmup)
+        out[f"decode_tok_s_b{b}"] = round(b / ms * 1e3, 1)
+        out[f"decode_ms_b{b}"] = round(ms, 4)
+        del r
+    out["kernels"] = _hybrid_kernels(model, prompt_len, batch)
+    return out
+
+
+def _hybrid_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
+    """Each family kernel alone, on the prompt shape (1 x T tokens) and the decode shape (batch x 1 token at context T)."""
+    from ..ops import hybrid as H
+
+    pk = _peaks()
+    dev, dt = model.device, model.dtype
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def rec(name: str, phase: str, ms: float, nbytes: float, flops: float) -> None:
+        rows.append({"kernel": name, "phase": phase, "ms": round(ms, 4), "gb_s": round(nbytes / ms / 1e6, 1),
+                     "tflops": round(flops / ms / 1e9, 2),
+                     "frac_of_roofline": round(max(nbytes / ms / 1e6 / pk["hbm_gbs"], flops / ms / 1e9 / pk["bf16_tflops"]), 4),
+                     "peaks": pk["source"]})
+
+    for phase, lengths, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [T] * batch)):
+        n_seq, N = len(lengths), sum(lengths)
+        pool = model.new_pool(n_seq, T + 8)
+        plan = H.BatchPlan.make(lengths, list(range(n_seq)), starts, dev)
+        for li, blk in enumerate(model.blocks[:3]):
+            mix, st = blk.mix, pool.runs[li]
+            h = torch.randn(N, model.config.width, device=dev).to(dt)
+            p = H.linear(h, mix.w_in)
+            if li == 0:
+                Hh, D, R, V, L = mix.H, mix.D, mix.R, mix.V, mix.L
+                st["cache"].normal_()
+                q = H.linear(H.norm_rows(mix.col(p, "dq"), mix.dq_norm, None, 1e-6, "rms", dt), mix.uq)
+                qlat = torch.randn(Hh, N, L, device=dev).to(dt)
+                ms = _time(lambda: H.latent_attn(qlat, q, st["cache"], plan, Hh, D, R, L, mix.scale), 5, 3, flush)
+                keys = sum((s + n) * n - n * (n - 1) // 2 for n, s in zip(lengths, starts))  # visible (query, key) pairs
+                nbytes = 2.0 * (2 * Hh * N * L + Hh * N * R) + 2.0 * (L + R) * sum(s + n for n, s in zip(lengths, starts))
+                rec("latent_attn", phase, ms, nbytes, 2.0 * Hh * keys * (2 * L + R))
+                ms = _time(lambda: H.latent_append(mix.col(p, "dkv"), q, mix.dkv_norm, mix.inv_freq, st["cache"], plan, Hh, D,
+                                                   R, L, mix.nrot, 1e-6), 5, 3, flush)
+                rec("latent_append", phase, ms, 2.0 * N * (2 * (L + R) + 2 * Hh * R), 0.0)
+            else:
+                mode = "delta" if li == 1 else "gla"
+                Hh, D, V = mix.H, mix.D, mix.V
+                G = mix.G if mode == "delta" else Hh
+                z = torch.randn(N, Hh * D, device=dev).to(dt)
+                gate = torch.randn(N, Hh * V, device=dev).to(dt)
+                if mode == "delta":
+                    c = H.conv_silu(p[:, :2 * G * D + Hh * V], mix.conv_w, st["conv"], plan)
+                    args = (c[:, :G * D], c[:, G * D:2 * G * D], c[:, 2 * G * D:], z, gate, mix.norm, st["state"], plan)
+                    kw = dict(heads=Hh, kv_heads=G, dim=D, vdim=V, mode=mode, eps=1e-6, zb=mix.dt_bias, beta=mix.col(p, "b"),
+                              a_log=mix.A_log)
+                    ms = _time(lambda: H.conv_silu(p[:, :2 * G * D + Hh * V], mix.conv_w, st["conv"], plan), 5, 3, flush)
+                    rec("conv_silu", phase, ms, 2.0 * N * 2 * (2 * G * D + Hh * V), 0.0)
+                else:
+                    args = (mix.col(p, "q"), mix.col(p, "k"), mix.col(p, "v"), z, gate, mix.norm, st["state"], plan)
+                    kw = dict(heads=Hh, kv_heads=G, dim=D, vdim=V, mode=mode, eps=1e-6, zb=mix.a2_b, tau=mix.tau)
+                ms = _time(lambda: H.gated_recurrence(*args, **kw), 5, 3, flush)
+                nbytes = 2.0 * N * (2 * G * D + Hh * D + 3 * Hh * V) + 8.0 * n_seq * Hh * D * V
+                rec(f"gated_recurrence[{mode}]", phase, ms, nbytes, (6.0 if mode == "delta" else 4.0) * N * Hh * D * V)
+        x = torch.randn(N, model.config.width, device=dev)
+        blk = model.blocks[0]
+        ms = _time(lambda: H.norm_rows(x, blk.norm1.w, blk.norm1.b, 1e-6, "layer", dt), 5, 3, flush)
+        rec("layer_norm", phase, ms, N * model.config.width * 6.0, 0.0)
+        del pool
+    return rows
+
+
+def _transformer(width: int, prompt_len: int, steps: int, warmup: int, target_params: float) -> Dict[str, Any]:
+    from ..models.config import Config
+    from ..models.stage import build_stage
+    from ..parallel.pipeline import DevicePipeline
+    from ..parallel.scheduler import SamplingParams
+    from ..utils.checkpoint import random_init_stage_
+
+    n_head = width // 128
+    groups = 8 if n_head % 8 == 0 else n_head
+    attn = width * (n_head + 2 * groups) * 128 + width * width
+    emb = 2 * 32000 * width
+    inter = int(max(256, round((target_params - emb - 4 * attn) / 4 / (3 * width) / 256) * 256))
+    cfg = Config(name="Llama-like-bench", block_size=prompt_len + steps + warmup + 64, vocab_size=32000, padded_vocab_size=32000,
+                 n_layer=4, n_head=n_head, n_embd=width, n_query_groups=groups, rotary_percentage=1.0, parallel_residual=False,
+                 bias=False, norm_class_name="RMSNorm", mlp_class_name="LLaMAMLP", intermediate_size=inter)
+    stage = build_stage(cfg, "starter", cfg.n_layer, meta=True)
+    random_init_stage_(stage, "cuda", torch.bfloat16)
+    params = sum(p.numel() for p in stage.parameters())
+    S = cfg.block_size
+    pipe = DevicePipeline(stage, 0, 1, n_samples=1, max_seq_length=S, sampling=SamplingParams.greedy(), max_prompt_len=prompt_len)
+    prompt = torch.randint(0, 32000, (prompt_len,), dtype=torch.int32)
+    out: Dict[str, Any] = {"params_m": round(params / 1e6, 1), "intermediate_size": inter}
+
+    def pre() -> None:
+        pipe.prepare([prompt], steps + warmup + 8)
+        torch.cuda.synchronize()
+
+    ts = []
+    for i in range(warmup + 5):
+        pre()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        pipe.prefill()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            ts.append(a.elapsed_time(b))
+    ts.sort()
+    ms = ts[len(ts) // 2]
+    out["prefill_tok_s"] = round(prompt_len / ms * 1e3, 1)
+    out["prefill_ms"] = round(ms, 3)
+    pipe.decode_rounds(warmup)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    pipe.decode_rounds(steps)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    out["decode_tok_s_b1"] = round(1e3 / ms, 1)
+    out["decode_ms_b1"] = round(ms, 4)
+    pipe.close()
+    return out
+
+
+def run_family_compare(widths: List[int], prompt_len: int = 2048, batch: int = 8, steps: int = 64, warmup: int = 8) -> Dict[str, Any]:
+    torch.backends.cuda.matmul.allow_tf32 = False
+    results = []
+    for w in widths:
+        hy = _hybrid(w, prompt_len, batch, steps, warmup)
+        torch.cuda.empty_cache()
+        try:
+            tr = _transformer(w, prompt_len, steps, warmup, hy["params_m"] * 1e6)
+        except Exception as e:  # noqa: BLE001 - the comparison arm must not hide the family's own numbers
+            tr = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
+        results.append({"width": w, "hybrid": hy, "transformer": tr})
+    return {"metric": "family_compare", "family": "hybrid", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+            "decode_batch": batch, "steps": steps, "warmup": warmup, "l2": "flushed between single-kernel timings",
+            "results": results}

@@ -70,8 +70,15 @@ def tol(dev):
 
 
 def close(got, want, dev, what=""):
-    err = (got.float().cpu() - want).abs().max().item()
-    assert err < tol(dev), f"{what}: max abs error {err}"
+    """fp32: every logit within 2e-4.  bf16 (activations rounded to 8 bits of mantissa between operations): the
+    error of each row, root mean square over the vocabulary, within 8 % of that row's own spread."""
+    diff = got.float().cpu() - want
+    if dev[1] == torch.float32:
+        err = diff.abs().max().item()
+        assert err < tol(dev), f"{what}: max abs error {err}"
+        return
+    rel = (diff.pow(2).mean(-1).sqrt() / want.std(-1).clamp_min(1e-3)).max().item()
+    assert rel < 0.08, f"{what}: relative rms error {rel}"
 
 
 def toks(n, vocab=50, seed=1):
