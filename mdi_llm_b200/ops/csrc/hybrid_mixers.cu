@@ -182,7 +182,8 @@ template <typename T>
 __global__ void latent_attn_kernel(const T* __restrict__ qlat, const T* __restrict__ q, long long q_stride,
                                    const T* __restrict__ cache, long long slot_stride, const int* __restrict__ meta,
                                    const int* __restrict__ tok_seq, T* __restrict__ out, int N, int H, int D, int R,
-                                   int L, float scale) {
+                                   int L, float scale, int nsplit, float* __restrict__ part_acc,
+                                   float* __restrict__ part_ml) {
   extern __shared__ float smem[];
   int Dk = L + R, ldk = Dk + 1;
   float* sq = smem;                       // [LAT_WARPS][Dk]
@@ -204,9 +205,14 @@ __global__ void latent_attn_kernel(const T* __restrict__ qlat, const T* __restri
 #pragma unroll
   for (int i = 0; i < LAT_MAXV; ++i) acc[i] = 0.f;
   int nv = (L + 31) / 32;
-  for (int t0 = 0; t0 < nkeys; t0 += LAT_TILE) {
+  // with nsplit > 1 (few query tokens, long contexts) block z scans only its share of the keys and leaves an
+  // unnormalised partial result; latent_combine_kernel merges the shares
+  int chunk = ((nkeys + nsplit - 1) / nsplit + LAT_TILE - 1) / LAT_TILE * LAT_TILE;
+  int k_begin = blockIdx.z * chunk, k_end = min(nkeys, k_begin + chunk);
+  __syncthreads();
+  for (int t0 = k_begin; t0 < k_end; t0 += LAT_TILE) {
     __syncthreads();
-    int lim = min(LAT_TILE, nkeys - t0);
+    int lim = min(LAT_TILE, k_end - t0);
     for (int idx = threadIdx.x; idx < lim * Dk; idx += blockDim.x) {
       int jj = idx / Dk, d = idx - jj * Dk;
       kt[jj * ldk + d] = to_f(rows[(size_t)(t0 + jj) * Dk + d]);
@@ -238,13 +244,48 @@ __global__ void latent_attn_kernel(const T* __restrict__ qlat, const T* __restri
     }
     mx = mnew;
   }
-  if (active) {
+  if (active && nsplit == 1) {
 #pragma unroll
     for (int i = 0; i < LAT_MAXV; ++i)
       if (i < nv) {
         int d = lane + 32 * i;
         if (d < L) out[((size_t)h * N + tok) * L + d] = from_f<T>(acc[i] / l);
       }
+  } else if (active) {
+    size_t base = ((size_t)blockIdx.z * H + h) * N + tok;
+#pragma unroll
+    for (int i = 0; i < LAT_MAXV; ++i)
+      if (i < nv) {
+        int d = lane + 32 * i;
+        if (d < L) part_acc[base * L + d] = acc[i];
+      }
+    if (lane == 0) {
+      part_ml[base * 2] = mx;
+      part_ml[base * 2 + 1] = l;
+    }
+  }
+}
+
+// out[h, tok] = sum_z acc_z e^(m_z - m) / sum_z l_z e^(m_z - m), m = max_z m_z (an empty share has m = -inf, l = 0)
+template <typename T>
+__global__ void latent_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                      T* __restrict__ out, int N, int H, int L, int nsplit) {
+  int tok = blockIdx.x, h = blockIdx.y;
+  float m = -INFINITY;
+  for (int z = 0; z < nsplit; ++z) m = fmaxf(m, part_ml[(((size_t)z * H + h) * N + tok) * 2]);
+  float den = 0.f;
+  for (int z = 0; z < nsplit; ++z) {
+    size_t b = ((size_t)z * H + h) * N + tok;
+    float lz = part_ml[b * 2 + 1];
+    if (lz > 0.f) den += lz * expf(part_ml[b * 2] - m);
+  }
+  for (int d = threadIdx.x; d < L; d += blockDim.x) {
+    float num = 0.f;
+    for (int z = 0; z < nsplit; ++z) {
+      size_t b = ((size_t)z * H + h) * N + tok;
+      if (part_ml[b * 2 + 1] > 0.f) num += part_acc[b * L + d] * expf(part_ml[b * 2] - m);
+    }
+    out[((size_t)h * N + tok) * L + d] = from_f<T>(num / den);
   }
 }
 
@@ -373,6 +414,100 @@ __global__ void gated_recurrence_kernel(RecArgs a) {
   for (int i = threadIdx.x; i < D * V; i += blockDim.x) gS[i] = S[i];
 }
 
+// The same recurrence with the state in registers: R lanes of a warp share one value column and own every R-th
+// key row of it (<= 32 rows each), partial sums meet through shuffles.  The sequential chain per token is D/R
+// instead of D steps and the state never touches shared memory.  Lanes are laid out [row group][column] inside a
+// warp so that a state row is read 32/R columns (one 32-byte sector at R = 4) at a time.
+#define REC_MAXROWS 32
+template <typename T, int R>
+__global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
+  constexpr int CPW = 32 / R;
+  extern __shared__ float smem[];
+  int D = a.D, V = a.V, h = blockIdx.y;
+  float* sq = smem;
+  float* sk = sq + D;
+  float* sa = sk + D;
+  float* red = sa + D;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int r = lane / CPW, j = warp * CPW + (lane % CPW);
+  bool col = j < V;
+  const int* m = a.meta + 4 * blockIdx.x;
+  int start = m[0], n = m[1];
+  float* gS = a.state + ((size_t)m[2] * a.H + h) * D * V;
+  float s[REC_MAXROWS];
+#pragma unroll
+  for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+    int i = r + R * ii;
+    s[ii] = (col && i < D) ? gS[(size_t)i * V + j] : 0.f;
+  }
+  int kvh = h / (a.H / a.G);
+  const T *q = (const T*)a.q, *k = (const T*)a.k, *v = (const T*)a.v, *z = (const T*)a.z, *g = (const T*)a.g;
+  const T *beta = (const T*)a.beta, *zb = (const T*)a.zb, *w = (const T*)a.w, *alog = (const T*)a.a_log;
+  T* out = (T*)a.out;
+  float rate = a.mode == 1 ? expf(to_f(alog[h])) : 0.f;
+  float dscale = 1.f / sqrtf((float)D);
+  for (int t = 0; t < n; ++t) {
+    size_t row = (size_t)start + t;
+    float pq = 0.f, pk = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      float qv = to_f(q[row * a.q_stride + kvh * D + i]);
+      float kv = to_f(k[row * a.k_stride + kvh * D + i]);
+      float zz = to_f(z[row * a.z_stride + h * D + i]) + (zb ? to_f(zb[h * D + i]) : 0.f);
+      sq[i] = qv;
+      sk[i] = kv;
+      sa[i] = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
+      pq += qv * qv;
+      pk += kv * kv;
+    }
+    float qs = dscale, ks = 1.f;
+    if (a.mode == 1) {
+      float sumq = block_sum(pq, red);
+      float sumk = block_sum(pk, red);
+      qs = dscale / sqrtf(sumq + 1e-6f);
+      ks = 1.f / sqrtf(sumk + 1e-6f);
+    } else {
+      __syncthreads();
+    }
+    float u = col ? to_f(v[row * a.v_stride + h * V + j]) : 0.f;
+    if (a.mode == 1) {
+      float rp = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+        int i = r + R * ii;
+        if (i < D) rp += sa[i] * s[ii] * (sk[i] * ks);
+      }
+#pragma unroll
+      for (int o = CPW; o < 32; o <<= 1) rp += __shfl_xor_sync(0xffffffffu, rp, o);
+      u = sigmoidf_(to_f(beta[row * a.beta_stride + h])) * (u - rp);
+    }
+    float o = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+      int i = r + R * ii;
+      if (i < D) {
+        float sv = sa[i] * s[ii] + (sk[i] * ks) * u;
+        s[ii] = sv;
+        o += sv * (sq[i] * qs);
+      }
+    }
+#pragma unroll
+    for (int off = CPW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+    float ss = block_sum((col && r == 0) ? o * o : 0.f, red);
+    if (col && r == 0) {
+      float y = o / sqrtf(ss / V + a.eps) * to_f(w[j]);
+      float gv = to_f(g[row * a.g_stride + h * V + j]);
+      y *= a.mode == 1 ? sigmoidf_(gv) : siluf_(gv);
+      out[row * a.out_stride + h * V + j] = from_f<T>(y);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+    int i = r + R * ii;
+    if (col && i < D) gS[(size_t)i * V + j] = s[ii];
+  }
+}
+
 }  // namespace hyb
 
 using namespace hyb;
@@ -471,23 +606,27 @@ int hyb_latent_append(const void* ckv, long long ckv_stride, void* q, long long 
 
 int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const void* cache, long long slot_stride,
                     const int* meta, const int* tok_seq, void* out, int N, int H, int D, int R, int L, float scale,
-                    int dt, cudaStream_t st) {
+                    int nsplit, float* part_acc, float* part_ml, int dt, cudaStream_t st) {
   if (N == 0) return 0;
-  if (L > 32 * LAT_MAXV) return -3;
+  if (L > 32 * LAT_MAXV || nsplit < 1 || (nsplit > 1 && (!part_acc || !part_ml))) return -3;
   int Dk = L + R;
   size_t smem = (size_t)(LAT_WARPS * Dk + LAT_TILE * (Dk + 1)) * sizeof(float);
   if (smem > 200 * 1024) return -3;
-  dim3 grid(N, (H + LAT_WARPS - 1) / LAT_WARPS);
+  dim3 grid(N, (H + LAT_WARPS - 1) / LAT_WARPS, nsplit);
   if (dt == 0) {
     cudaFuncSetAttribute(latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     latent_attn_kernel<bf16><<<grid, LAT_WARPS * 32, smem, st>>>((const bf16*)qlat, (const bf16*)q, q_stride,
                                                                  (const bf16*)cache, slot_stride, meta, tok_seq,
-                                                                 (bf16*)out, N, H, D, R, L, scale);
+                                                                 (bf16*)out, N, H, D, R, L, scale, nsplit, part_acc,
+                                                                 part_ml);
+    if (nsplit > 1) latent_combine_kernel<bf16><<<dim3(N, H), 128, 0, st>>>(part_acc, part_ml, (bf16*)out, N, H, L, nsplit);
   } else {
     cudaFuncSetAttribute(latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     latent_attn_kernel<float><<<grid, LAT_WARPS * 32, smem, st>>>((const float*)qlat, (const float*)q, q_stride,
                                                                   (const float*)cache, slot_stride, meta, tok_seq,
-                                                                  (float*)out, N, H, D, R, L, scale);
+                                                                  (float*)out, N, H, D, R, L, scale, nsplit, part_acc,
+                                                                  part_ml);
+    if (nsplit > 1) latent_combine_kernel<float><<<dim3(N, H), 128, 0, st>>>(part_acc, part_ml, (float*)out, N, H, L, nsplit);
   }
   return (int)cudaGetLastError();
 }
@@ -508,10 +647,32 @@ int hyb_conv_silu(const void* x, long long x_stride, const void* w, void* state,
   return (int)cudaGetLastError();
 }
 
-int hyb_gated_recurrence(const RecArgs* args, int nseq, int dt, cudaStream_t st) {
+}  // extern "C"
+
+template <typename T, int R>
+static int launch_rec_reg(const RecArgs& a, int nseq, cudaStream_t st) {
+  int cpw = 32 / R;
+  int threads = (a.V + cpw - 1) / cpw * 32;
+  size_t smem = ((size_t)3 * a.D + 33) * sizeof(float);
+  gated_recurrence_reg_kernel<T, R><<<dim3(nseq, a.H), threads, smem, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" {
+
+// variant: 0 = choose (registers when the shape fits, else shared memory), 1 = shared-memory kernel, 2 = registers
+int hyb_gated_recurrence(const RecArgs* args, int nseq, int dt, int variant, cudaStream_t st) {
   if (nseq == 0) return 0;
   RecArgs a = *args;
   if (a.V > 1024 || a.H % a.G) return -3;
+  int R = 0;
+  if (variant != 1) {
+    if (a.D <= 4 * REC_MAXROWS && a.V <= 128) R = 4;       // V * 4 <= 512 threads
+    else if (a.D <= 8 * REC_MAXROWS && a.V <= 64) R = 8;   // V * 8 <= 512 threads
+  }
+  if (variant == 2 && R == 0) return -3;
+  if (R == 4) return dt == 0 ? launch_rec_reg<bf16, 4>(a, nseq, st) : launch_rec_reg<float, 4>(a, nseq, st);
+  if (R == 8) return dt == 0 ? launch_rec_reg<bf16, 8>(a, nseq, st) : launch_rec_reg<float, 8>(a, nseq, st);
   size_t smem = ((size_t)a.D * a.V + 3 * a.D + 33) * sizeof(float);
   if (smem > 220 * 1024) return -3;
   int threads = (a.V + 31) / 32 * 32;

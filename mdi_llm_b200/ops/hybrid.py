@@ -65,9 +65,9 @@ def lib() -> ctypes.CDLL:
     h.hyb_headmajor_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
     h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
-    h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
+    h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
-    h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, vp]
+    h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, vp]
     _lib = h
     return h
 
@@ -271,11 +271,14 @@ def latent_append(ckv: torch.Tensor, q: torch.Tensor, w: torch.Tensor, inv_freq:
                                    nrot, eps, _dt(ckv), _st()), "latent_append")
 
 
+_SM_TARGET = 148  # one block per SM of a B200
+
+
 def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: BatchPlan, H: int, D: int, R: int, L: int,
-                scale: float) -> torch.Tensor:
+                scale: float, split: int = 0) -> torch.Tensor:
     """Causal softmax attention of ``H`` heads over the cached rows ``[L latent | R rotated key]`` of each token's slot.
     The query of head ``h`` is ``[qlat[h, tok] | q[tok, h, D:]]``, the value of a row is its latent part.
-    Returns the attended latents ``[H, N, L]``."""
+    Returns the attended latents ``[H, N, L]``.  ``split`` (CUDA): key shares per query, 0 = chosen from the batch shape."""
     N = q.size(0)
     if not q.is_cuda:
         out = torch.empty(H, N, L, dtype=q.dtype)
@@ -291,8 +294,18 @@ def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: 
     assert qlat.is_contiguous()
     qs, _ = _rows(q)
     out = torch.empty(H, N, L, device=q.device, dtype=q.dtype)
+    # few query tokens (decoding) cannot fill the GPU with one block per token and 8 heads: split the keys of each
+    # query over several blocks and merge the partial softmaxes.  The split count depends only on the batch shape,
+    # so a captured step stays valid while contexts grow.
+    blocks = N * ((H + 7) // 8)
+    nsplit = 1 if blocks >= 2 * _SM_TARGET or split == 1 else (split or max(1, min(32, (2 * _SM_TARGET) // blocks)))
+    pa = pm = None
+    if nsplit > 1:
+        pa = torch.empty(nsplit, H, N, L, device=q.device, dtype=torch.float32)
+        pm = torch.empty(nsplit, H, N, 2, device=q.device, dtype=torch.float32)
     _check(lib().hyb_latent_attn(qlat.data_ptr(), q.data_ptr(), qs, cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
-                                 plan.tok_seq.data_ptr(), out.data_ptr(), N, H, D, R, L, float(scale), _dt(q), _st()),
+                                 plan.tok_seq.data_ptr(), out.data_ptr(), N, H, D, R, L, float(scale), nsplit,
+                                 None if pa is None else pa.data_ptr(), None if pm is None else pm.data_ptr(), _dt(q), _st()),
            "latent_attn")
     return out
 
@@ -325,14 +338,16 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, plan: Batch
 def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, g: torch.Tensor,
                      w: torch.Tensor, state: torch.Tensor, plan: BatchPlan, *, heads: int, kv_heads: int, dim: int,
                      vdim: int, mode: str, eps: float, zb: Optional[torch.Tensor] = None, tau: float = 1.0,
-                     beta: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     beta: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None, variant: int = 0) -> torch.Tensor:
     """A linear recurrence with a ``[dim, vdim]`` fp32 state per head and slot, read out, normed and gated.
 
     ``mode="gla"``:   ``a = sigmoid(z + zb)^(1/tau)``; ``S = diag(a) S + k v^T``; ``o = S^T q / sqrt(dim)``; gate SiLU.
     ``mode="delta"``: ``a = exp(-exp(a_log) softplus(z + zb))``; q, k made unit vectors (eps 1e-6);
     ``S = diag(a) S``; ``u = sigmoid(beta) (v - S^T k)``; ``S += k u^T``; ``o = S^T q / sqrt(dim)``; gate sigmoid.
     Output per head: ``o / rms(o) * w * gate(g)``, rows ``[N, heads * vdim]``.  ``state [slots, heads, dim, vdim]``
-    is read at the start of the step and written back at its end.
+    is read at the start of the step and written back at its end.  ``variant`` (CUDA only): 0 picks the kernel that
+    keeps the state in registers when ``dim <= 256`` and ``vdim <= 256`` fit it and the shared-memory kernel
+    otherwise, 1 and 2 force one of them.
     """
     N = v.size(0)
     H, G, D, V = heads, kv_heads, dim, vdim
@@ -382,5 +397,5 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch
     a.out_stride = H * V
     a.H, a.G, a.D, a.V, a.mode = H, G, D, V, 1 if mode == "delta" else 0
     a.tau, a.eps = float(tau), float(eps)
-    _check(lib().hyb_gated_recurrence(ctypes.byref(a), len(plan.seqs), _dt(v), _st()), "gated_recurrence")
+    _check(lib().hyb_gated_recurrence(ctypes.byref(a), len(plan.seqs), _dt(v), int(variant), _st()), "gated_recurrence")
     return out

@@ -143,7 +143,7 @@ class HybridRunner(StageRunner):
         g.load([int(t[0]) for _, t in entries], slots, pos)
         g.graph.replay()
         self._advance(g.plan)
-        return g.logits
+        return g.logits.clone()  # the graph's output buffer is overwritten by the next replay
 
     # ---- StageRunner interface (one sample per call) ----------------------------------------------
     @torch.inference_mode()

@@ -73,7 +73,7 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int) ->
     cfg = HybridConfig.from_dict(hybrid_bench_config(width))
     model = HybridLM(cfg, {}).init_random(dev, torch.bfloat16, seed=1)
     params = sum(p.numel() for p in model.tensor_map().values())
-    out: Dict[str, Any] = {"params_m": round(params / 1e6, 1)}
+    out: Dict[str, Any] = {"params_m": round(params / 1e6, 1), "layer_params_m": round((params - model.embed.numel()) / 1e6, 1)}
     prompt = torch.randint(0, cfg.vocab, (prompt_len,)).tolist()
     S = prompt_len + steps + warmup + 8
 
@@ -174,8 +174,7 @@ def _transformer(width: int, prompt_len: int, steps: int, warmup: int, target_pa
     n_head = width // 128
     groups = 8 if n_head % 8 == 0 else n_head
     attn = width * (n_head + 2 * groups) * 128 + width * width
-    emb = 2 * 32000 * width
-    inter = int(max(256, round((target_params - emb - 4 * attn) / 4 / (3 * width) / 256) * 256))
+    inter = int(max(256, round((target_params / 4 - attn) / (3 * width) / 256) * 256))  # equal parameters per layer
     cfg = Config(name="Llama-like-bench", block_size=prompt_len + steps + warmup + 64, vocab_size=32000, padded_vocab_size=32000,
                  n_layer=4, n_head=n_head, n_embd=width, n_query_groups=groups, rotary_percentage=1.0, parallel_residual=False,
                  bias=False, norm_class_name="RMSNorm", mlp_class_name="LLaMAMLP", intermediate_size=inter)
@@ -185,7 +184,8 @@ def _transformer(width: int, prompt_len: int, steps: int, warmup: int, target_pa
     S = cfg.block_size
     pipe = DevicePipeline(stage, 0, 1, n_samples=1, max_seq_length=S, sampling=SamplingParams.greedy(), max_prompt_len=prompt_len)
     prompt = torch.randint(0, 32000, (prompt_len,), dtype=torch.int32)
-    out: Dict[str, Any] = {"params_m": round(params / 1e6, 1), "intermediate_size": inter}
+    layer_params = sum(p.numel() for p in stage.transformer.h.parameters())
+    out: Dict[str, Any] = {"params_m": round(params / 1e6, 1), "layer_params_m": round(layer_params / 1e6, 1), "intermediate_size": inter}
 
     def pre() -> None:
         pipe.prepare([prompt], steps + warmup + 8)
@@ -226,7 +226,7 @@ def run_family_compare(widths: List[int], prompt_len: int = 2048, batch: int = 8
         hy = _hybrid(w, prompt_len, batch, steps, warmup)
         torch.cuda.empty_cache()
         try:
-            tr = _transformer(w, prompt_len, steps, warmup, hy["params_m"] * 1e6)
+            tr = _transformer(w, prompt_len, steps, warmup, hy["layer_params_m"] * 1e6)
         except Exception as e:  # noqa: BLE001 - the comparison arm must not hide the family's own numbers
             tr = {"error": f"{type(e).__name__}: {e}"}
         torch.cuda.empty_cache()

@@ -316,3 +316,70 @@ def test_sequence_longer_than_pool_is_refused():
     r = HybridRunner(m, 8)
     with pytest.raises(ValueError):
         r.step([("a", toks(9))])
+
+
+# ---- kernel variants against each other and against the PyTorch bodies (GPU only) --------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(3, 1, 24, 20), (4, 4, 128, 128), (2, 1, 200, 64), (2, 2, 40, 300)], ids=str)
+@pytest.mark.parametrize("mode", ["gla", "delta"])
+def test_recurrence_kernels_agree(dtype, shape, mode):
+    from mdi_llm_b200.ops import hybrid as H
+
+    heads, kv, D, V = shape
+    g = torch.Generator().manual_seed(0)
+    lengths, starts = [5, 1, 17], [0, 0, 0]
+    N = sum(lengths)
+
+    def rnd(*s, scale=1.0):
+        return (torch.randn(*s, generator=g) * scale).to(torch.bfloat16).float()
+
+    t = dict(q=rnd(N, kv * D), k=rnd(N, kv * D), v=rnd(N, heads * V), z=rnd(N, heads * D), gate=rnd(N, heads * V),
+             w=1 + rnd(V, scale=0.1), zb=rnd(heads * D), beta=rnd(N, heads), a_log=rnd(heads, scale=0.3))
+    state0 = rnd(3, heads, D, V, scale=0.2)
+
+    def run(device, dt, variant):
+        x = {k: v.to(device=device, dtype=dt) for k, v in t.items()}
+        st = state0.clone().to(device)
+        plan = BatchPlan.make(lengths, [2, 0, 1], starts, torch.device(device))
+        kw = dict(heads=heads, kv_heads=kv, dim=D, vdim=V, mode=mode, eps=1e-5, zb=x["zb"])
+        if mode == "delta":
+            kw.update(beta=x["beta"], a_log=x["a_log"])
+        else:
+            kw.update(tau=5.0)
+        if device == "cuda":
+            kw["variant"] = variant
+        y = H.gated_recurrence(x["q"], x["k"], x["v"], x["z"], x["gate"], x["w"], st, plan, **kw)
+        return y.float().cpu(), st.cpu()
+
+    want_y, want_s = run("cpu", torch.float32, 0)
+    variants = [1] + ([2] if (D <= 128 and V <= 128) or (D <= 256 and V <= 64) else [])
+    for variant in variants:
+        y, s = run("cuda", dtype, variant)
+        lim = 2e-4 if dtype == torch.float32 else 0.06
+        assert (y - want_y).abs().max() < lim * max(1.0, want_y.abs().max().item()), f"variant {variant} output"
+        assert (s - want_s).abs().max() < lim * max(1.0, want_s.abs().max().item()), f"variant {variant} state"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_split_key_attention_matches_unsplit_and_finds_one_far_key(dtype):
+    from mdi_llm_b200.ops import hybrid as H
+
+    Hh, D, R, L = 5, 16, 8, 40
+    ctx = [700, 33, 1]
+    g = torch.Generator().manual_seed(0)
+    cache = (torch.randn(3, 704, L + R, generator=g) * 0.3).to(torch.bfloat16).float()
+    qlat = (torch.randn(Hh, 3, L, generator=g) * 0.3).to(torch.bfloat16).float()
+    q = (torch.randn(3, Hh * (D + R), generator=g) * 0.3).to(torch.bfloat16).float()
+    # head 2 of sequence 0 looks for key 3: a copy of that key, scaled up, as its query
+    qlat[2, 0] = cache[0, 3, :L] * 40
+    plan_c = BatchPlan.make([1, 1, 1], [0, 1, 2], [c - 1 for c in ctx], torch.device("cpu"))
+    want = H.latent_attn(qlat, q, cache, plan_c, Hh, D, R, L, 0.25)
+    assert (want[2, 0] - cache[0, 3, :L]).abs().max() < 1e-2  # the far key really dominates
+    plan = BatchPlan.make([1, 1, 1], [0, 1, 2], [c - 1 for c in ctx], torch.device("cuda"))
+    args = [x.cuda().to(dtype) for x in (qlat, q, cache)]
+    lim = 1e-5 if dtype == torch.float32 else 2e-2
+    for split in (1, 0, 7, 32):
+        got = H.latent_attn(args[0], args[1], args[2], plan, Hh, D, R, L, 0.25, split=split).float().cpu()
+        assert (got - want).abs().max() < lim, f"split {split}"
