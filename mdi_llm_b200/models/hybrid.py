@@ -188,10 +188,41 @@ class LatentAttention(nn.Module, _Fused):
         cq = H.norm_rows(self.col(p, "dq"), self.dq_norm, None, self.eps, "rms", h.dtype)
         q = H.linear(cq, self.uq)
         H.latent_append(self.col(p, "dkv"), q, self.dkv_norm, self.inv_freq, st["cache"], plan, Hh, D, R, L, self.nrot, self.eps)
-        qlat = torch.bmm(q.view(N, Hh, D + R)[:, :, :D].transpose(0, 1), self.uk.view(Hh, D, L)).contiguous()
-        olat = H.latent_attn(qlat, q, st["cache"], plan, Hh, D, R, L, self.scale)
-        o = torch.bmm(olat, self.uv.view(Hh, V, L).transpose(1, 2)).contiguous()
+        if min(n for _, n, _, _ in plan.seqs) >= self.expand_from:
+            o = self._expanded(q, st["cache"], plan)
+        else:
+            qlat = torch.bmm(q.view(N, Hh, D + R)[:, :, :D].transpose(0, 1), self.uk.view(Hh, D, L)).contiguous()
+            olat = H.latent_attn(qlat, q, st["cache"], plan, Hh, D, R, L, self.scale)
+            o = torch.bmm(olat, self.uv.view(Hh, V, L).transpose(1, 2)).contiguous()
         return H.linear(H.headmajor_gate(o, self.col(p, "g")), self.o)
+
+    expand_from = 64   # a step whose every sequence brings at least this many tokens takes the expanded form
+    query_block = 1024  # rows of the score matrix alive at a time
+
+    def _expanded(self, q: torch.Tensor, cache: torch.Tensor, plan: H.BatchPlan) -> torch.Tensor:
+        """Prompt form: keys and values are expanded from the cached latents once per step (two matrix products),
+        scores and the weighted sum are batched matrix products over heads, the causal softmax runs on fp32 scores.
+        Decoding instead carries the query into the latent space and reads the cache directly (``H.latent_attn``):
+        per query that costs ``kv_rank`` instead of ``dim`` multiplies per key and head, which only pays when
+        there is a single query.  Returns ``[heads, N, vdim]``."""
+        Hh, D, R, V, L = self.H, self.D, self.R, self.V, self.L
+        out = torch.empty(Hh, q.size(0), V, device=q.device, dtype=q.dtype)
+        for r0, n, slot, p0 in plan.seqs:
+            keys = p0 + n
+            rows = cache[slot, :keys]
+            lat = rows[:, :L]
+            k = torch.empty(Hh, D + R, keys, device=q.device, dtype=q.dtype)  # K^T per head: [unrotated | shared rotated]
+            k[:, :D] = H.linear(lat, self.uk).view(keys, Hh, D).permute(1, 2, 0)
+            k[:, D:] = rows[:, L:].t()
+            v = H.linear(lat, self.uv).view(keys, Hh, V).transpose(0, 1)  # [H, keys, V]
+            qh = q[r0:r0 + n].view(n, Hh, D + R).transpose(0, 1)  # [H, n, D+R]
+            for a in range(0, n, self.query_block):
+                b = min(n, a + self.query_block)
+                vis = p0 + b  # keys any row of this block can see
+                s = H.matmul_f32(qh[:, a:b], k[:, :, :vis]).contiguous()
+                pr = H.causal_softmax(s, p0 + a, self.scale, q.dtype)
+                out[:, r0 + a:r0 + b] = torch.bmm(pr, v[:, :vis])
+        return out
 
 
 class GatedLinearAttention(nn.Module, _Fused):

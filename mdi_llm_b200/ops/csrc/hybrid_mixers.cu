@@ -289,6 +289,33 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
   }
 }
 
+// Causal softmax of fp32 score rows for the expanded (prompt) form of latent attention: row (h, i) sees keys
+// j <= first_pos + i; p = softmax(scale * s) over those, zeros elsewhere, written in the activation type.
+template <typename T>
+__global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict__ p, int rows_per_head, int keys,
+                                      int first_pos, float scale) {
+  __shared__ float red[33];
+  size_t row = blockIdx.x;
+  int i = (int)(row % rows_per_head);
+  int vis = min(keys, first_pos + i + 1);
+  const float* src = s + row * keys;
+  T* dst = p + row * keys;
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, src[j]);
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = -INFINITY;
+  for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
+  sum = block_sum(sum, red);
+  float inv = 1.f / sum;
+  for (int j = threadIdx.x; j < keys; j += blockDim.x)
+    dst[j] = from_f<T>(j < vis ? expf((src[j] - m) * scale) * inv : 0.f);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // short causal convolution + SiLU over packed sequences, with the last taps-1 inputs kept per slot
 // ---------------------------------------------------------------------------------------------------------
@@ -446,10 +473,39 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
   T* out = (T*)a.out;
   float rate = a.mode == 1 ? expf(to_f(alog[h])) : 0.f;
   float dscale = 1.f / sqrtf((float)D);
+  // the inputs of token t + 1 are requested before token t is computed, so the chain from one token to the next
+  // holds arithmetic and barriers only, no global-memory latency
+  int i0 = threadIdx.x;
+  bool has0 = i0 < D, lead = col && r == 0;
+  float nq = 0.f, nk = 0.f, nz = 0.f, nu = 0.f, ng = 0.f, nb = 0.f;
+  float zb0 = (has0 && zb) ? to_f(zb[h * D + i0]) : 0.f;
+  float wj = lead ? to_f(w[j]) : 0.f;
+  auto fetch = [&](int t) {
+    size_t row = (size_t)start + t;
+    if (has0) {
+      nq = to_f(q[row * a.q_stride + kvh * D + i0]);
+      nk = to_f(k[row * a.k_stride + kvh * D + i0]);
+      nz = to_f(z[row * a.z_stride + h * D + i0]);
+    }
+    if (col) nu = to_f(v[row * a.v_stride + h * V + j]);
+    if (lead) ng = to_f(g[row * a.g_stride + h * V + j]);
+    if (a.mode == 1) nb = to_f(beta[row * a.beta_stride + h]);
+  };
+  if (n > 0) fetch(0);
   for (int t = 0; t < n; ++t) {
     size_t row = (size_t)start + t;
+    float cq = nq, ck = nk, cz = nz, u = nu, gv = ng, bt = nb;
+    if (t + 1 < n) fetch(t + 1);
     float pq = 0.f, pk = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    if (has0) {
+      float zz = cz + zb0;
+      sq[i0] = cq;
+      sk[i0] = ck;
+      sa[i0] = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
+      pq = cq * cq;
+      pk = ck * ck;
+    }
+    for (int i = i0 + blockDim.x; i < D; i += blockDim.x) {  // D larger than the block: the rest, not prefetched
       float qv = to_f(q[row * a.q_stride + kvh * D + i]);
       float kv = to_f(k[row * a.k_stride + kvh * D + i]);
       float zz = to_f(z[row * a.z_stride + h * D + i]) + (zb ? to_f(zb[h * D + i]) : 0.f);
@@ -468,7 +524,6 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
     } else {
       __syncthreads();
     }
-    float u = col ? to_f(v[row * a.v_stride + h * V + j]) : 0.f;
     if (a.mode == 1) {
       float rp = 0.f;
 #pragma unroll
@@ -478,7 +533,7 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
       }
 #pragma unroll
       for (int o = CPW; o < 32; o <<= 1) rp += __shfl_xor_sync(0xffffffffu, rp, o);
-      u = sigmoidf_(to_f(beta[row * a.beta_stride + h])) * (u - rp);
+      u = sigmoidf_(bt) * (u - rp);
     }
     float o = 0.f;
 #pragma unroll
@@ -492,14 +547,12 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
     }
 #pragma unroll
     for (int off = CPW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-    float ss = block_sum((col && r == 0) ? o * o : 0.f, red);
-    if (col && r == 0) {
-      float y = o / sqrtf(ss / V + a.eps) * to_f(w[j]);
-      float gv = to_f(g[row * a.g_stride + h * V + j]);
+    float ss = block_sum(lead ? o * o : 0.f, red);  // its barriers also fence sq/sk/sa before the next token
+    if (lead) {
+      float y = o / sqrtf(ss / V + a.eps) * wj;
       y *= a.mode == 1 ? sigmoidf_(gv) : siluf_(gv);
       out[row * a.out_stride + h * V + j] = from_f<T>(y);
     }
-    __syncthreads();
   }
 #pragma unroll
   for (int ii = 0; ii < REC_MAXROWS; ++ii) {
@@ -628,6 +681,15 @@ int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const v
                                                                   part_ml);
     if (nsplit > 1) latent_combine_kernel<float><<<dim3(N, H), 128, 0, st>>>(part_acc, part_ml, (float*)out, N, H, L, nsplit);
   }
+  return (int)cudaGetLastError();
+}
+
+int hyb_causal_softmax(const float* s, void* p, long long rows, int rows_per_head, int keys, int first_pos, float scale,
+                       int dt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (scale <= 0.f) return -3;  // the row maximum is taken before scaling
+  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale)),
+               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale)));
   return (int)cudaGetLastError();
 }
 

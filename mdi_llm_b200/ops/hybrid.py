@@ -27,7 +27,7 @@ import torch.nn.functional as F
 from . import build as _build
 
 __all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
-           "headmajor_gate", "softcap", "latent_append", "latent_attn", "conv_silu", "gated_recurrence", "linear",
+           "headmajor_gate", "softcap", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
            "rotary_inv_freq"]
 
 
@@ -66,6 +66,7 @@ def lib() -> ctypes.CDLL:
     h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
     h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
+    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
     h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, vp]
     _lib = h
@@ -308,6 +309,32 @@ def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: 
                                  None if pa is None else pa.data_ptr(), None if pm is None else pm.data_ptr(), _dt(q), _st()),
            "latent_attn")
     return out
+
+
+def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``softmax(scale * scores)`` over the visible keys of fp32 ``scores [heads, rows, keys]``: row ``i`` sees keys
+    ``j <= first_pos + i``; hidden keys get probability 0.  Result in ``out_dtype``."""
+    Hh, n, keys = scores.shape
+    if not scores.is_cuda:
+        j = torch.arange(keys)
+        hidden = j[None, None, :] > (first_pos + torch.arange(n))[None, :, None]
+        return torch.softmax((scores.float() * scale).masked_fill(hidden, float("-inf")), -1).to(out_dtype)
+    if scores.dtype != torch.float32 or not scores.is_contiguous():
+        raise HybridOpsError("scores are dense fp32")
+    p = torch.empty(Hh, n, keys, device=scores.device, dtype=out_dtype)
+    _check(lib().hyb_causal_softmax(scores.data_ptr(), p.data_ptr(), Hh * n, n, keys, int(first_pos), float(scale), _dt(p), _st()),
+           "causal_softmax")
+    return p
+
+
+def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Batched ``a @ b`` with an fp32 result whatever the operand type (scores that feed a softmax)."""
+    if a.dtype == torch.float32:
+        return torch.bmm(a, b)
+    try:
+        return torch.bmm(a, b, out_dtype=torch.float32)
+    except (TypeError, RuntimeError):
+        return torch.bmm(a.float(), b.float())
 
 
 # ---------------------------------------------------------------------------------------------------------
