@@ -21,6 +21,20 @@ template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+__device__ __forceinline__ void load8(const float* p, float* f) {
+  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* f) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -213,9 +227,20 @@ __global__ void latent_attn_kernel(const T* __restrict__ qlat, const T* __restri
   for (int t0 = k_begin; t0 < k_end; t0 += LAT_TILE) {
     __syncthreads();
     int lim = min(LAT_TILE, k_end - t0);
-    for (int idx = threadIdx.x; idx < lim * Dk; idx += blockDim.x) {
-      int jj = idx / Dk, d = idx - jj * Dk;
-      kt[jj * ldk + d] = to_f(rows[(size_t)(t0 + jj) * Dk + d]);
+    if ((Dk & 7) == 0 && (((size_t)rows) & 15) == 0) {  // 8 values per load (16 bytes of bf16, 2 x 16 of fp32)
+      int per = Dk >> 3;
+      for (int idx = threadIdx.x; idx < lim * per; idx += blockDim.x) {
+        int jj = idx / per, d = (idx - jj * per) << 3;
+        float f[8];
+        load8(rows + (size_t)(t0 + jj) * Dk + d, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kt[jj * ldk + d + e] = f[e];
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < lim * Dk; idx += blockDim.x) {
+        int jj = idx / Dk, d = idx - jj * Dk;
+        kt[jj * ldk + d] = to_f(rows[(size_t)(t0 + jj) * Dk + d]);
+      }
     }
     __syncthreads();
     if (!active) continue;
@@ -477,24 +502,26 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
   // holds arithmetic and barriers only, no global-memory latency
   int i0 = threadIdx.x;
   bool has0 = i0 < D, lead = col && r == 0;
-  float nq = 0.f, nk = 0.f, nz = 0.f, nu = 0.f, ng = 0.f, nb = 0.f;
+  // prefetched values stay in their storage type: a conversion right after the load would make the (in-order)
+  // warp wait for the load at once, which is exactly the latency the prefetch is there to hide
+  T nq = from_f<T>(0.f), nk = nq, nz = nq, nu = nq, ng = nq, nb = nq;
   float zb0 = (has0 && zb) ? to_f(zb[h * D + i0]) : 0.f;
   float wj = lead ? to_f(w[j]) : 0.f;
   auto fetch = [&](int t) {
     size_t row = (size_t)start + t;
     if (has0) {
-      nq = to_f(q[row * a.q_stride + kvh * D + i0]);
-      nk = to_f(k[row * a.k_stride + kvh * D + i0]);
-      nz = to_f(z[row * a.z_stride + h * D + i0]);
+      nq = q[row * a.q_stride + kvh * D + i0];
+      nk = k[row * a.k_stride + kvh * D + i0];
+      nz = z[row * a.z_stride + h * D + i0];
     }
-    if (col) nu = to_f(v[row * a.v_stride + h * V + j]);
-    if (lead) ng = to_f(g[row * a.g_stride + h * V + j]);
-    if (a.mode == 1) nb = to_f(beta[row * a.beta_stride + h]);
+    if (col) nu = v[row * a.v_stride + h * V + j];
+    if (lead) ng = g[row * a.g_stride + h * V + j];
+    if (a.mode == 1) nb = beta[row * a.beta_stride + h];
   };
   if (n > 0) fetch(0);
   for (int t = 0; t < n; ++t) {
     size_t row = (size_t)start + t;
-    float cq = nq, ck = nk, cz = nz, u = nu, gv = ng, bt = nb;
+    float cq = to_f(nq), ck = to_f(nk), cz = to_f(nz), u = col ? to_f(nu) : 0.f, gv = to_f(ng), bt = to_f(nb);
     if (t + 1 < n) fetch(t + 1);
     float pq = 0.f, pk = 0.f;
     if (has0) {

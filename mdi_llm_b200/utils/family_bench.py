@@ -130,10 +130,20 @@ def _hybrid_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
                 st["cache"].normal_()
                 q = H.linear(H.norm_rows(mix.col(p, "dq"), mix.dq_norm, None, 1e-6, "rms", dt), mix.uq)
                 qlat = torch.randn(Hh, N, L, device=dev).to(dt)
-                ms = _time(lambda: H.latent_attn(qlat, q, st["cache"], plan, Hh, D, R, L, mix.scale), 5, 3, flush)
                 keys = sum((s + n) * n - n * (n - 1) // 2 for n, s in zip(lengths, starts))  # visible (query, key) pairs
-                nbytes = 2.0 * (2 * Hh * N * L + Hh * N * R) + 2.0 * (L + R) * sum(s + n for n, s in zip(lengths, starts))
-                rec("latent_attn", phase, ms, nbytes, 2.0 * Hh * keys * (2 * L + R))
+                if phase == "prefill":  # prompts take the expanded form: GEMMs + the causal softmax kernel
+                    ms = _time(lambda: mix._expanded(q, st["cache"], plan), 5, 3, flush)
+                    total_keys = sum(s + n for n, s in zip(lengths, starts))
+                    flops = 2.0 * total_keys * L * Hh * (D + V) + 2.0 * Hh * keys * (D + R + V)
+                    rec("latent_attn_expanded(gemm+softmax)", phase, ms, 2.0 * N * Hh * (D + R + V), flops)
+                    s32 = torch.randn(Hh, min(N, 1024), N, device=dev)
+                    ms = _time(lambda: H.causal_softmax(s32, N - s32.size(1), mix.scale, dt), 5, 3, flush)
+                    rec("causal_softmax", phase, ms, s32.numel() * 6.0, 0.0)
+                    del s32
+                else:
+                    ms = _time(lambda: H.latent_attn(qlat, q, st["cache"], plan, Hh, D, R, L, mix.scale), 5, 3, flush)
+                    nbytes = 2.0 * (2 * Hh * N * L + Hh * N * R) + 2.0 * (L + R) * sum(s + n for n, s in zip(lengths, starts))
+                    rec("latent_attn", phase, ms, nbytes, 2.0 * Hh * keys * (2 * L + R))
                 ms = _time(lambda: H.latent_append(mix.col(p, "dkv"), q, mix.dkv_norm, mix.inv_freq, st["cache"], plan, Hh, D,
                                                    R, L, mix.nrot, 1e-6), 5, 3, flush)
                 rec("latent_append", phase, ms, 2.0 * N * (2 * (L + R) + 2 * Hh * R), 0.0)
