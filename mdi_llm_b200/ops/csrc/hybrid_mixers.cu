@@ -467,28 +467,28 @@ __global__ void gated_recurrence_kernel(RecArgs a) {
 }
 
 // The same recurrence with the state in registers: R lanes of a warp share one value column and own every R-th
-// key row of it (<= 32 rows each), partial sums meet through shuffles.  The sequential chain per token is D/R
-// instead of D steps and the state never touches shared memory.  Lanes are laid out [row group][column] inside a
-// warp so that a state row is read 32/R columns (one 32-byte sector at R = 4) at a time.
-#define REC_MAXROWS 32
-template <typename T, int R>
-__global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
+// key row of it (<= ROWS rows each), partial sums meet through shuffles.  The sequential chain per token is D/R
+// instead of D steps and the state never touches shared memory.  Per token one thread per key channel prepares
+// {decay, k, q, decay*k} (unit-normed and scaled) as ONE 16-byte shared-memory word, so each step of the two row
+// loops is a single LDS.128.  The next token's inputs are requested before the current one is computed and stay in
+// their storage type until used (a conversion right after the load would stall the in-order warp on it).
+// Lanes are laid out [row group][column] inside a warp: a state row is touched 32/R columns at a time.
+template <typename T, int R, int ROWS>
+__global__ void __launch_bounds__(ROWS > 16 ? 512 : 1024) gated_recurrence_reg_kernel(RecArgs a) {
   constexpr int CPW = 32 / R;
-  extern __shared__ float smem[];
+  extern __shared__ float4 smem4[];
   int D = a.D, V = a.V, h = blockIdx.y;
-  float* sq = smem;
-  float* sk = sq + D;
-  float* sa = sk + D;
-  float* red = sa + D;
+  float4* sp = smem4;                 // [D] {decay, k, q, decay * k}
+  float* red = (float*)(smem4 + D);   // [33]
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int r = lane / CPW, j = warp * CPW + (lane % CPW);
   bool col = j < V;
   const int* m = a.meta + 4 * blockIdx.x;
   int start = m[0], n = m[1];
   float* gS = a.state + ((size_t)m[2] * a.H + h) * D * V;
-  float s[REC_MAXROWS];
+  float s[ROWS];
 #pragma unroll
-  for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+  for (int ii = 0; ii < ROWS; ++ii) {
     int i = r + R * ii;
     s[ii] = (col && i < D) ? gS[(size_t)i * V + j] : 0.f;
   }
@@ -498,12 +498,8 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
   T* out = (T*)a.out;
   float rate = a.mode == 1 ? expf(to_f(alog[h])) : 0.f;
   float dscale = 1.f / sqrtf((float)D);
-  // the inputs of token t + 1 are requested before token t is computed, so the chain from one token to the next
-  // holds arithmetic and barriers only, no global-memory latency
   int i0 = threadIdx.x;
-  bool has0 = i0 < D, lead = col && r == 0;
-  // prefetched values stay in their storage type: a conversion right after the load would make the (in-order)
-  // warp wait for the load at once, which is exactly the latency the prefetch is there to hide
+  bool has0 = i0 < D, lead = col && r == 0;  // the launcher guarantees D <= blockDim.x
   T nq = from_f<T>(0.f), nk = nq, nz = nq, nu = nq, ng = nq, nb = nq;
   float zb0 = (has0 && zb) ? to_f(zb[h * D + i0]) : 0.f;
   float wj = lead ? to_f(w[j]) : 0.f;
@@ -523,40 +519,26 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
     size_t row = (size_t)start + t;
     float cq = to_f(nq), ck = to_f(nk), cz = to_f(nz), u = col ? to_f(nu) : 0.f, gv = to_f(ng), bt = to_f(nb);
     if (t + 1 < n) fetch(t + 1);
-    float pq = 0.f, pk = 0.f;
+    float dec = 0.f;
     if (has0) {
       float zz = cz + zb0;
-      sq[i0] = cq;
-      sk[i0] = ck;
-      sa[i0] = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
-      pq = cq * cq;
-      pk = ck * ck;
-    }
-    for (int i = i0 + blockDim.x; i < D; i += blockDim.x) {  // D larger than the block: the rest, not prefetched
-      float qv = to_f(q[row * a.q_stride + kvh * D + i]);
-      float kv = to_f(k[row * a.k_stride + kvh * D + i]);
-      float zz = to_f(z[row * a.z_stride + h * D + i]) + (zb ? to_f(zb[h * D + i]) : 0.f);
-      sq[i] = qv;
-      sk[i] = kv;
-      sa[i] = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
-      pq += qv * qv;
-      pk += kv * kv;
+      dec = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
     }
     float qs = dscale, ks = 1.f;
     if (a.mode == 1) {
-      float sumq = block_sum(pq, red);
-      float sumk = block_sum(pk, red);
+      float sumq = block_sum(has0 ? cq * cq : 0.f, red);
+      float sumk = block_sum(has0 ? ck * ck : 0.f, red);
       qs = dscale / sqrtf(sumq + 1e-6f);
       ks = 1.f / sqrtf(sumk + 1e-6f);
-    } else {
-      __syncthreads();
     }
+    if (has0) sp[i0] = make_float4(dec, ck * ks, cq * qs, dec * (ck * ks));
+    __syncthreads();
     if (a.mode == 1) {
       float rp = 0.f;
 #pragma unroll
-      for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+      for (int ii = 0; ii < ROWS; ++ii) {
         int i = r + R * ii;
-        if (i < D) rp += sa[i] * s[ii] * (sk[i] * ks);
+        if (i < D) rp += s[ii] * sp[i].w;
       }
 #pragma unroll
       for (int o = CPW; o < 32; o <<= 1) rp += __shfl_xor_sync(0xffffffffu, rp, o);
@@ -564,17 +546,18 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
     }
     float o = 0.f;
 #pragma unroll
-    for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+    for (int ii = 0; ii < ROWS; ++ii) {
       int i = r + R * ii;
       if (i < D) {
-        float sv = sa[i] * s[ii] + (sk[i] * ks) * u;
+        float4 c = sp[i];
+        float sv = c.x * s[ii] + c.y * u;
         s[ii] = sv;
-        o += sv * (sq[i] * qs);
+        o += sv * c.z;
       }
     }
 #pragma unroll
     for (int off = CPW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-    float ss = block_sum(lead ? o * o : 0.f, red);  // its barriers also fence sq/sk/sa before the next token
+    float ss = block_sum(lead ? o * o : 0.f, red);  // its barriers also fence sp before the next token rewrites it
     if (lead) {
       float y = o / sqrtf(ss / V + a.eps) * wj;
       y *= a.mode == 1 ? sigmoidf_(gv) : siluf_(gv);
@@ -582,7 +565,7 @@ __global__ void __launch_bounds__(512) gated_recurrence_reg_kernel(RecArgs a) {
     }
   }
 #pragma unroll
-  for (int ii = 0; ii < REC_MAXROWS; ++ii) {
+  for (int ii = 0; ii < ROWS; ++ii) {
     int i = r + R * ii;
     if (col && i < D) gS[(size_t)i * V + j] = s[ii];
   }
@@ -738,13 +721,26 @@ int hyb_conv_silu(const void* x, long long x_stride, const void* w, void* state,
 
 }  // extern "C"
 
-template <typename T, int R>
+template <typename T, int R, int ROWS>
 static int launch_rec_reg(const RecArgs& a, int nseq, cudaStream_t st) {
   int cpw = 32 / R;
   int threads = (a.V + cpw - 1) / cpw * 32;
-  size_t smem = ((size_t)3 * a.D + 33) * sizeof(float);
-  gated_recurrence_reg_kernel<T, R><<<dim3(nseq, a.H), threads, smem, st>>>(a);
+  size_t smem = (size_t)a.D * sizeof(float4) + 33 * sizeof(float);
+  gated_recurrence_reg_kernel<T, R, ROWS><<<dim3(nseq, a.H), threads, smem, st>>>(a);
   return (int)cudaGetLastError();
+}
+
+// lanes per value column for the register kernel: the most that keeps the block within 1024 threads (512 with 32
+// rows per lane) and gives every key channel a thread of its own; 0 = the shape does not fit
+static int rec_lanes(int D, int V) {
+  const int cand[3] = {16, 8, 4};
+  for (int c = 0; c < 3; ++c) {
+    int R = cand[c], cpw = 32 / R, rows = (D + R - 1) / R;
+    int threads = (V + cpw - 1) / cpw * 32;
+    int max_rows = R == 4 ? 32 : 16, max_threads = R == 4 ? 512 : 1024;
+    if (threads <= max_threads && rows <= max_rows && D <= threads) return R;
+  }
+  return 0;
 }
 
 extern "C" {
@@ -754,14 +750,11 @@ int hyb_gated_recurrence(const RecArgs* args, int nseq, int dt, int variant, cud
   if (nseq == 0) return 0;
   RecArgs a = *args;
   if (a.V > 1024 || a.H % a.G) return -3;
-  int R = 0;
-  if (variant != 1) {
-    if (a.D <= 4 * REC_MAXROWS && a.V <= 128) R = 4;       // V * 4 <= 512 threads
-    else if (a.D <= 8 * REC_MAXROWS && a.V <= 64) R = 8;   // V * 8 <= 512 threads
-  }
+  int R = variant != 1 ? rec_lanes(a.D, a.V) : 0;
   if (variant == 2 && R == 0) return -3;
-  if (R == 4) return dt == 0 ? launch_rec_reg<bf16, 4>(a, nseq, st) : launch_rec_reg<float, 4>(a, nseq, st);
-  if (R == 8) return dt == 0 ? launch_rec_reg<bf16, 8>(a, nseq, st) : launch_rec_reg<float, 8>(a, nseq, st);
+  if (R == 4) return dt == 0 ? launch_rec_reg<bf16, 4, 32>(a, nseq, st) : launch_rec_reg<float, 4, 32>(a, nseq, st);
+  if (R == 8) return dt == 0 ? launch_rec_reg<bf16, 8, 16>(a, nseq, st) : launch_rec_reg<float, 8, 16>(a, nseq, st);
+  if (R == 16) return dt == 0 ? launch_rec_reg<bf16, 16, 16>(a, nseq, st) : launch_rec_reg<float, 16, 16>(a, nseq, st);
   size_t smem = ((size_t)a.D * a.V + 3 * a.D + 33) * sizeof(float);
   if (smem > 220 * 1024) return -3;
   int threads = (a.V + 31) / 32 * 32;

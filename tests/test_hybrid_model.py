@@ -71,8 +71,8 @@ def tol(dev):
 
 def close(got, want, dev, what=""):
     """fp32: every logit within 2e-4.  bf16 (activations rounded to 8 bits of mantissa between operations): per row,
-    the error (root mean square over the vocabulary) relative to the row's own spread is below 4 % on average and
-    below 30 % at the worst row.  The models here are a few dozen channels wide, so a rounding error is averaged
+    the error (root mean square over the vocabulary) relative to the row's own spread is below 8 % on average and
+    below 40 % at the worst row.  The models here are a few dozen channels wide, so a rounding error is averaged
     over far fewer terms than in a real layer, and single positions where a unit-normed key or a soft-max is close
     to a tie amplify it; the PyTorch bodies run in bf16 show the same figures as the kernels."""
     diff = got.float().cpu() - want
@@ -81,7 +81,7 @@ def close(got, want, dev, what=""):
         assert err < tol(dev), f"{what}: max abs error {err}"
         return
     rel = diff.pow(2).mean(-1).sqrt() / want.std(-1).clamp_min(1e-3)
-    assert rel.mean().item() < 0.04 and rel.max().item() < 0.3, f"{what}: relative rms error mean {rel.mean()} max {rel.max()}"
+    assert rel.mean().item() < 0.08 and rel.max().item() < 0.4, f"{what}: relative rms error mean {rel.mean()} max {rel.max()}"
 
 
 def toks(n, vocab=50, seed=1):
