@@ -571,6 +571,136 @@ __global__ void __launch_bounds__(ROWS > 16 ? 512 : 1024) gated_recurrence_reg_k
   }
 }
 
+// ---- prompts: the recurrence as three kernels, so that the sequential part holds nothing but the recurrence ----
+// (1) rec_prep: everything that does not depend on the state, for all tokens in parallel: decay, unit-normed and
+//     scaled q and k, decay * k as one float4 per (token, head, key channel); sigmoid(beta) per (token, head).
+// (2) rec_scan: the scan itself.  Value columns never interact, so a head's columns are spread over blockIdx.z
+//     blocks (more SMs busy, fewer warps per step); per token: stage D float4 (double-buffered, ONE barrier),
+//     two short row loops from registers, shuffles, raw fp32 read-out.
+// (3) rec_finish: per (token, head) RMS norm of the read-out, weight, gate, cast — parallel over tokens again.
+template <typename T>
+__global__ void rec_prep_kernel(RecArgs a, float4* __restrict__ prep, float* __restrict__ bsig) {
+  __shared__ float red[33];
+  int tok = blockIdx.x, h = blockIdx.y, D = a.D;
+  int kvh = h / (a.H / a.G);
+  const T *q = (const T*)a.q, *k = (const T*)a.k, *z = (const T*)a.z, *zb = (const T*)a.zb;
+  float rate = a.mode == 1 ? expf(to_f(((const T*)a.a_log)[h])) : 0.f;
+  float pq = 0.f, pk = 0.f;
+  if (a.mode == 1) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      float qv = to_f(q[(size_t)tok * a.q_stride + kvh * D + i]), kv = to_f(k[(size_t)tok * a.k_stride + kvh * D + i]);
+      pq += qv * qv;
+      pk += kv * kv;
+    }
+    pq = block_sum(pq, red);
+    pk = block_sum(pk, red);
+  }
+  float dscale = 1.f / sqrtf((float)D);
+  float qs = a.mode == 1 ? dscale / sqrtf(pq + 1e-6f) : dscale;
+  float ks = a.mode == 1 ? 1.f / sqrtf(pk + 1e-6f) : 1.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float qv = to_f(q[(size_t)tok * a.q_stride + kvh * D + i]), kv = to_f(k[(size_t)tok * a.k_stride + kvh * D + i]);
+    float zz = to_f(z[(size_t)tok * a.z_stride + h * D + i]) + (zb ? to_f(zb[h * D + i]) : 0.f);
+    float dec = a.mode == 1 ? expf(-rate * softplusf_(zz)) : expf(-softplusf_(-zz) / a.tau);
+    prep[((size_t)tok * a.H + h) * D + i] = make_float4(dec, kv * ks, qv * qs, dec * (kv * ks));
+  }
+  if (a.mode == 1 && threadIdx.x == 0)
+    bsig[(size_t)tok * a.H + h] = sigmoidf_(to_f(((const T*)a.beta)[(size_t)tok * a.beta_stride + h]));
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(256) rec_scan_kernel(RecArgs a, const float4* __restrict__ prep,
+                                                       const float* __restrict__ bsig, float* __restrict__ oraw,
+                                                       int cols_per_block) {
+  constexpr int CPW = 32 / R;
+  constexpr int ROWS = 16;
+  extern __shared__ float4 smem4[];  // [2][D]
+  int D = a.D, V = a.V, h = blockIdx.y;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int r = lane / CPW, jl = warp * CPW + (lane % CPW);
+  int j = blockIdx.z * cols_per_block + jl;
+  bool col = jl < cols_per_block && j < V;
+  bool lead = col && r == 0;
+  const int* m = a.meta + 4 * blockIdx.x;
+  int start = m[0], n = m[1];
+  float* gS = a.state + ((size_t)m[2] * a.H + h) * D * V;
+  float s[ROWS];
+#pragma unroll
+  for (int ii = 0; ii < ROWS; ++ii) {
+    int i = r + R * ii;
+    s[ii] = (col && i < D) ? gS[(size_t)i * V + j] : 0.f;
+  }
+  const T* v = (const T*)a.v;
+  int i0 = threadIdx.x;
+  bool has0 = i0 < D;  // the launcher guarantees D <= blockDim.x
+  float4 n4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  T nu = from_f<T>(0.f);
+  float nb = 0.f;
+  auto fetch = [&](int t) {
+    size_t row = (size_t)start + t;
+    if (has0) n4 = prep[(row * a.H + h) * D + i0];
+    if (col) nu = v[row * a.v_stride + h * V + j];
+    if (a.mode == 1) nb = bsig[row * a.H + h];
+  };
+  if (n > 0) fetch(0);
+  for (int t = 0; t < n; ++t) {
+    size_t row = (size_t)start + t;
+    float4* sp = smem4 + (t & 1) * D;
+    if (has0) sp[i0] = n4;
+    float u = col ? to_f(nu) : 0.f, bt = nb;
+    if (t + 1 < n) fetch(t + 1);
+    __syncthreads();  // the only barrier per token: the other buffer was last read before the previous barrier
+    if (a.mode == 1) {
+      float rp = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < ROWS; ++ii) {
+        int i = r + R * ii;
+        if (i < D) rp += s[ii] * sp[i].w;
+      }
+#pragma unroll
+      for (int o = CPW; o < 32; o <<= 1) rp += __shfl_xor_sync(0xffffffffu, rp, o);
+      u = bt * (u - rp);
+    }
+    float o = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < ROWS; ++ii) {
+      int i = r + R * ii;
+      if (i < D) {
+        float4 c = sp[i];
+        float sv = c.x * s[ii] + c.y * u;
+        s[ii] = sv;
+        o += sv * c.z;
+      }
+    }
+#pragma unroll
+    for (int off = CPW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+    if (lead) oraw[row * ((size_t)a.H * V) + h * V + j] = o;
+  }
+#pragma unroll
+  for (int ii = 0; ii < ROWS; ++ii) {
+    int i = r + R * ii;
+    if (col && i < D) gS[(size_t)i * V + j] = s[ii];
+  }
+}
+
+template <typename T>
+__global__ void rec_finish_kernel(RecArgs a, const float* __restrict__ oraw) {
+  __shared__ float red[33];
+  int tok = blockIdx.x, h = blockIdx.y, V = a.V;
+  const float* o = oraw + (size_t)tok * a.H * V + h * V;
+  const T *g = (const T*)a.g, *w = (const T*)a.w;
+  T* out = (T*)a.out;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) ss += o[j] * o[j];
+  ss = block_sum(ss, red);
+  float inv = 1.f / sqrtf(ss / V + a.eps);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    float gv = to_f(g[(size_t)tok * a.g_stride + h * V + j]);
+    float y = o[j] * inv * to_f(w[j]) * (a.mode == 1 ? sigmoidf_(gv) : siluf_(gv));
+    out[(size_t)tok * a.out_stride + h * V + j] = from_f<T>(y);
+  }
+}
+
 }  // namespace hyb
 
 using namespace hyb;
@@ -745,11 +875,40 @@ static int rec_lanes(int D, int V) {
 
 extern "C" {
 
-// variant: 0 = choose (registers when the shape fits, else shared memory), 1 = shared-memory kernel, 2 = registers
-int hyb_gated_recurrence(const RecArgs* args, int nseq, int dt, int variant, cudaStream_t st) {
+// variant: 0 = choose, 1 = shared-memory kernel, 2 = register kernel, 3 = prepare / scan / finish (needs the three
+// work buffers: prep [N, H, D] float4, bsig [N, H] float, oraw [N, H * V] float).  "Choose" takes 3 for steps that
+// bring more tokens than sequences (prompts) when the buffers are given and D <= 256, else 2 when the shape fits,
+// else 1.
+int hyb_gated_recurrence(const RecArgs* args, int nseq, int N, int dt, int variant, void* prep, float* bsig,
+                         float* oraw, cudaStream_t st) {
   if (nseq == 0) return 0;
   RecArgs a = *args;
   if (a.V > 1024 || a.H % a.G) return -3;
+  bool can3 = prep && bsig && oraw && a.D <= 256;
+  if (variant == 3 && !can3) return -3;
+  if (variant == 3 || (variant == 0 && can3 && N > nseq)) {
+    int R = a.D <= 128 ? 8 : 16, cpw = 32 / R;
+    int cols = 256 / R;                       // value columns per block at 256 threads
+    if (cols > a.V) cols = (a.V + cpw - 1) / cpw * cpw;
+    int vs = (a.V + cols - 1) / cols;
+    int threads = cols / cpw * 32;
+    int need = (a.D + 31) / 32 * 32;          // one staging thread per key channel
+    if (threads < need) threads = need;
+    size_t smem = 2 * (size_t)a.D * sizeof(float4);
+    dim3 g1(N, a.H), g2(nseq, a.H, vs);
+    if (dt == 0) {
+      rec_prep_kernel<bf16><<<g1, 128, 0, st>>>(a, (float4*)prep, bsig);
+      if (R == 8) rec_scan_kernel<bf16, 8><<<g2, threads, smem, st>>>(a, (const float4*)prep, bsig, oraw, cols);
+      else rec_scan_kernel<bf16, 16><<<g2, threads, smem, st>>>(a, (const float4*)prep, bsig, oraw, cols);
+      rec_finish_kernel<bf16><<<g1, 128, 0, st>>>(a, oraw);
+    } else {
+      rec_prep_kernel<float><<<g1, 128, 0, st>>>(a, (float4*)prep, bsig);
+      if (R == 8) rec_scan_kernel<float, 8><<<g2, threads, smem, st>>>(a, (const float4*)prep, bsig, oraw, cols);
+      else rec_scan_kernel<float, 16><<<g2, threads, smem, st>>>(a, (const float4*)prep, bsig, oraw, cols);
+      rec_finish_kernel<float><<<g1, 128, 0, st>>>(a, oraw);
+    }
+    return (int)cudaGetLastError();
+  }
   int R = variant != 1 ? rec_lanes(a.D, a.V) : 0;
   if (variant == 2 && R == 0) return -3;
   if (R == 4) return dt == 0 ? launch_rec_reg<bf16, 4, 32>(a, nseq, st) : launch_rec_reg<float, 4, 32>(a, nseq, st);

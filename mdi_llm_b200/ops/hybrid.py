@@ -68,7 +68,7 @@ def lib() -> ctypes.CDLL:
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
     h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
-    h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, vp]
+    h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, i32, vp, vp, vp, vp]
     _lib = h
     return h
 
@@ -372,9 +372,10 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch
     ``mode="delta"``: ``a = exp(-exp(a_log) softplus(z + zb))``; q, k made unit vectors (eps 1e-6);
     ``S = diag(a) S``; ``u = sigmoid(beta) (v - S^T k)``; ``S += k u^T``; ``o = S^T q / sqrt(dim)``; gate sigmoid.
     Output per head: ``o / rms(o) * w * gate(g)``, rows ``[N, heads * vdim]``.  ``state [slots, heads, dim, vdim]``
-    is read at the start of the step and written back at its end.  ``variant`` (CUDA only): 0 picks the kernel that
-    keeps the state in registers when ``dim <= 256`` and ``vdim <= 256`` fit it and the shared-memory kernel
-    otherwise, 1 and 2 force one of them.
+    is read at the start of the step and written back at its end.  ``variant`` (CUDA only): 0 chooses — steps that
+    bring more tokens than sequences (prompts) run as prepare / scan / finish kernels (3) when ``dim <= 256``,
+    one-token steps as the fused kernel with the state in registers (2) when the shape fits it, anything else as the
+    fused kernel with the state in shared memory (1); 1, 2, 3 force one.
     """
     N = v.size(0)
     H, G, D, V = heads, kv_heads, dim, vdim
@@ -424,5 +425,12 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch
     a.out_stride = H * V
     a.H, a.G, a.D, a.V, a.mode = H, G, D, V, 1 if mode == "delta" else 0
     a.tau, a.eps = float(tau), float(eps)
-    _check(lib().hyb_gated_recurrence(ctypes.byref(a), len(plan.seqs), _dt(v), int(variant), _st()), "gated_recurrence")
+    prep = bsig = oraw = None
+    if variant in (0, 3) and D <= 256 and (variant == 3 or N > len(plan.seqs)):
+        prep = torch.empty(N, H, D, 4, device=v.device, dtype=torch.float32)
+        bsig = torch.empty(N, H, device=v.device, dtype=torch.float32)
+        oraw = torch.empty(N, H * V, device=v.device, dtype=torch.float32)
+    _check(lib().hyb_gated_recurrence(ctypes.byref(a), len(plan.seqs), N, _dt(v), int(variant),
+                                      None if prep is None else prep.data_ptr(), None if bsig is None else bsig.data_ptr(),
+                                      None if oraw is None else oraw.data_ptr(), _st()), "gated_recurrence")
     return out

@@ -357,6 +357,7 @@ def test_recurrence_kernels_agree(dtype, shape, mode):
 
     want_y, want_s = run("cpu", torch.float32, 0)
     variants = [1] + ([2] if (D <= 128 and V <= 128) or (D <= 256 and V <= 64) else [])
+    variants += [3, 0]  # prepare / scan / finish kernels, and whatever the dispatcher picks for this step
     for variant in variants:
         y, s = run("cuda", dtype, variant)
         lim = 2e-4 if dtype == torch.float32 else 0.06
