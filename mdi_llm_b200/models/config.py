@@ -212,7 +212,17 @@ MIXER_KEYS = {
     "latent_attention": ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "scale", "rot"),
     "gla": ("heads", "dim", "vdim", "tau"),
     "channel_delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
+    "attention": ("heads", "kv_heads", "dim", "vdim", "scale"),
 }
+
+# What an architecture of the family fixes beyond its config.json: the shape of a block ("sandwich": norms before and
+# after each sublayer; "prenorm": one norm before, the sublayer output times ``residual_mult`` added), the kind of
+# its norms, and whether the output head is the embedding table or a tensor of its own.
+ARCHITECTURE_TRAITS = {
+    "Badapel": {"block": "sandwich", "norm": "layer", "tied_head": True},
+    "Vudelix": {"block": "prenorm", "norm": "rms", "tied_head": False},
+}
+FF_KINDS = ("dense", "moe")
 
 
 @dataclass
@@ -223,6 +233,12 @@ class HybridConfig:
     ``loop = {"start", "stop", "times"}`` repeats layers ``start..stop-1`` ``times`` times with shared weights and a
     state of its own per pass; each pass starts with a re-injection of the embedding output.  Everything a model
     of the family may vary is a field; nothing is assumed from a particular checkpoint.
+
+    A feed-forward is ``{"kind": "dense", "ff": n}`` or a mixture of experts ``{"kind": "moe", "expert": {"ff": n},
+    "router": {"experts": E, "top": k}}``.  ``residual_mult`` scales every sublayer output before it joins the
+    residual stream (pre-norm blocks); ``token_side = {"dim": d}`` gives every layer a second, per-layer embedding of
+    the current token (a ``d``-wide slice of one table) that is gated by the residual stream and added to it.
+    ``block``, ``norm`` and ``tied_head`` come from :data:`ARCHITECTURE_TRAITS` unless given.
     """
 
     architecture: str = "Badapel"
@@ -233,8 +249,22 @@ class HybridConfig:
     norm_eps: float = 1e-6
     logit_softcap: float = 0.0
     name: str = ""
+    residual_mult: float = 1.0
+    token_side: Optional[dict] = None
+    block: str = ""
+    norm: str = ""
+    tied_head: Optional[bool] = None
 
     def __post_init__(self) -> None:
+        traits = ARCHITECTURE_TRAITS.get(self.architecture, ARCHITECTURE_TRAITS["Badapel"])
+        self.block = self.block or traits["block"]
+        self.norm = self.norm or traits["norm"]
+        if self.tied_head is None:
+            self.tied_head = traits["tied_head"]
+        if self.block not in ("sandwich", "prenorm") or self.norm not in ("layer", "rms"):
+            raise ValueError(f"unknown block {self.block!r} or norm {self.norm!r}")
+        if self.token_side is not None and int(self.token_side.get("dim", 0)) <= 0:
+            raise ValueError("token_side needs a positive dim")
         if self.vocab <= 0 or self.width <= 0 or not self.layers:
             raise ValueError("a hybrid config needs vocab, width and at least one layer")
         for i, spec in enumerate(self.layers):
@@ -245,8 +275,15 @@ class HybridConfig:
             if missing:
                 raise ValueError(f"layer {i} ({kind}): missing mixer fields {missing}")
             mlp = spec.get("mlp")
-            if mlp is not None and mlp.get("kind") != "dense":
+            if mlp is not None and mlp.get("kind") not in FF_KINDS:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+            if mlp is not None and mlp["kind"] == "moe":
+                r = mlp.get("router", {})
+                if not (1 <= int(r.get("top", 0)) <= int(r.get("experts", 0))) or int(mlp.get("expert", {}).get("ff", 0)) <= 0:
+                    raise ValueError(f"layer {i}: a mixture of experts needs expert.ff and 1 <= router.top <= router.experts")
+            m = spec["mixer"]
+            if kind in ("attention", "channel_delta") and int(m["heads"]) % int(m["kv_heads"]):
+                raise ValueError(f"layer {i}: heads must be a multiple of kv_heads")
         if self.loop is not None:
             a, b, t = self.loop["start"], self.loop["stop"], self.loop["times"]
             if not (0 <= a < b <= len(self.layers)) or t < 1:
@@ -282,7 +319,9 @@ class HybridConfig:
         return cls(architecture=d.get("architecture", "Badapel"), vocab=int(d["vocab"]), width=int(d["width"]),
                    layers=[dict(x) for x in d["layers"]], loop=dict(d["loop"]) if d.get("loop") else None,
                    norm_eps=float(d.get("norm", {}).get("eps", 1e-6)),
-                   logit_softcap=float(d.get("logit_softcap") or 0.0), name=d.get("name", ""))
+                   logit_softcap=float(d.get("logit_softcap") or 0.0), name=d.get("name", ""),
+                   residual_mult=float(d.get("residual_mult", 1.0)),
+                   token_side=dict(d["token_side"]) if d.get("token_side") else None)
 
     @classmethod
     def from_file(cls, path: Union[str, Path]) -> "HybridConfig":
@@ -298,6 +337,10 @@ class HybridConfig:
             out["loop"] = self.loop
         if self.logit_softcap:
             out["logit_softcap"] = self.logit_softcap
+        if self.residual_mult != 1.0:
+            out["residual_mult"] = self.residual_mult
+        if self.token_side is not None:
+            out["token_side"] = self.token_side
         return out
 
     def save(self, checkpoint_dir: Union[str, Path]) -> Path:

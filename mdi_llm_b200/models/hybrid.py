@@ -10,9 +10,15 @@ Mixers (all written against the packed-batch operations of :mod:`mdi_llm_b200.op
   channel.
 * :class:`ChannelDelta` — the gated delta rule with a decay per key channel, short causal convolutions on q, k, v
   and unit-norm q, k.
+* :class:`WindowAttention` — grouped-query softmax attention over a sliding window of cached keys and values, with
+  interleaved rotary positions (optionally stretched by wavelength), weight-free RMS norm of q and k after the
+  rotation, and one sigmoid output gate per head.
 
-A layer is a *sandwich* block: ``x += norm_b(f(norm_a(x)))`` for the mixer and again for the feed-forward, with
-the residual stream kept in fp32.  A span of layers may be looped; each pass owns its own state and starts by
+Feed-forwards: :class:`DenseFF` and :class:`MoEFF` (sigmoid router, top-k, the score scales the expert's *input*).
+
+A layer is a *sandwich* block (``x += norm_b(f(norm_a(x)))`` for the mixer and again for the feed-forward) or a
+*pre-norm* block (``x += m f(norm(x))``, optionally followed by a gated per-layer token embedding), chosen by the
+architecture (``config.block``), with the residual stream kept in fp32.  A span of layers may be looped; each pass owns its own state and starts by
 mixing the embedding output back in.  State lives in a :class:`StatePool` — slots like the KV pool of the
 transformer family (``models/gpt.py:KVPool``), one entry per *layer run*.
 """
@@ -29,8 +35,8 @@ import torch.nn as nn
 from ..ops import hybrid as H
 from .config import HybridConfig
 
-__all__ = ["HybridLM", "StatePool", "SandwichBlock", "LatentAttention", "GatedLinearAttention", "ChannelDelta",
-           "DenseFF", "read_safetensors", "write_safetensors", "load_hybrid"]
+__all__ = ["HybridLM", "StatePool", "SandwichBlock", "PreNormBlock", "LatentAttention", "GatedLinearAttention",
+           "ChannelDelta", "WindowAttention", "DenseFF", "MoEFF", "read_safetensors", "write_safetensors", "load_hybrid"]
 
 _ST_DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32, "I64": torch.int64}
 
@@ -95,6 +101,8 @@ class StatePool:
         m = spec["mixer"]
         if spec["type"] == "latent_attention":
             return {"cache": ((self.max_seq_length, m["kv_rank"] + m["rot_dim"]), self.dtype)}
+        if spec["type"] == "attention":  # one row per position: the kv_heads keys, then the kv_heads values
+            return {"cache": ((self.max_seq_length, m["kv_heads"] * (m["dim"] + m["vdim"])), self.dtype)}
         out = {"state": ((m["heads"], m["dim"], m["vdim"]), torch.float32)}
         if spec["type"] == "channel_delta" and m["conv"] > 1:
             ch = 2 * m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"]
@@ -284,6 +292,116 @@ class ChannelDelta(nn.Module, _Fused):
         return H.linear(y, self.o)
 
 
+class WindowAttention(nn.Module, _Fused):
+    """Grouped-query attention over the last ``window`` positions (0: all earlier ones) of the slot's cache."""
+
+    tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+    expand_from = 64   # a step whose every sequence brings at least this many tokens runs as banded matrix products
+    query_block = 512  # query rows per band
+
+    def __init__(self, width: int, m: Dict[str, Any], eps: float) -> None:
+        super().__init__()
+        self.H, self.G, self.D, self.V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        self.scale, self.eps = float(m["scale"]), eps
+        self.window = int((m.get("mask") or {}).get("size", 0) or 0)
+        rot = m.get("rot") or {}
+        self.nrot, self.rot_base, self.rot_scaling = int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), rot.get("scaling")
+        if self.nrot > self.D or self.nrot % 2:
+            raise ValueError("rot.dims must be even and at most dim")
+        Hh, G, D, V = self.H, self.G, self.D, self.V
+        self.q, self.k, self.v = _param(Hh * D, width), _param(G * D, width), _param(G * V, width)
+        self.g, self.o = _param(Hh, width), _param(width, Hh * V)
+        self.inv_freq: Optional[torch.Tensor] = None
+
+    def finalize(self) -> None:
+        self.fuse(("q", "k", "v", "g"))
+        if self.nrot:
+            self.inv_freq = H.scaled_inv_freq(self.nrot, self.rot_base, self.rot_scaling, self.q.device)
+
+    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
+        p = H.linear(h, self.w_in)
+        q, g = self.col(p, "q"), self.col(p, "g")
+        H.window_append(q, self.col(p, "k"), self.col(p, "v"), self.inv_freq, st["cache"], plan, self.H, self.G, self.D,
+                        self.V, self.nrot, self.eps)
+        if min(n for _, n, _, _ in plan.seqs) >= self.expand_from:
+            o = H.head_gate(self._banded(q, st["cache"], plan), g)
+        else:
+            o = H.window_attn(q, g, st["cache"], plan, self.H, self.G, self.D, self.V, self.scale, self.window)
+        return H.linear(o, self.o)
+
+    def _banded(self, q: torch.Tensor, cache: torch.Tensor, plan: H.BatchPlan) -> torch.Tensor:
+        """Prompt form: per block of query rows, scores against the band of keys the block can see and the weighted
+        sum are batched matrix products over the key/value heads (the query heads of a group stacked as rows), the
+        masked softmax runs on fp32 scores.  Returns ``[heads, N, vdim]``."""
+        Hh, G, D, V, W = self.H, self.G, self.D, self.V, self.window
+        rep = Hh // G
+        out = torch.empty(Hh, q.size(0), V, device=q.device, dtype=q.dtype)
+        for r0, n, slot, p0 in plan.seqs:
+            for a in range(0, n, self.query_block):
+                b = min(n, a + self.query_block)
+                nb = b - a
+                key0 = max(0, p0 + a - W + 1) if W > 0 else 0
+                rows = cache[slot, key0:p0 + b]
+                keys = rows.size(0)
+                kt = rows[:, :G * D].view(keys, G, D).permute(1, 2, 0)   # [G, D, keys]
+                vv = rows[:, G * D:].view(keys, G, V).transpose(0, 1)     # [G, keys, V]
+                qh = q[r0 + a:r0 + b].view(nb, G, rep, D).permute(1, 2, 0, 3).reshape(G, rep * nb, D)
+                s = H.matmul_f32(qh, kt).contiguous()
+                pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, q.dtype, window=W, key0=key0)
+                out[:, r0 + a:r0 + b] = torch.bmm(pr.view(G, rep * nb, keys), vv).view(Hh, nb, V)
+        return out
+
+
+class MoEFF(nn.Module):
+    """``sum over the top-k experts e of down_e relu(up_e (s_e h))^2`` with ``s = sigmoid(router h)`` in fp32.
+
+    The expert weights are stacked (``up [E, ff, C]``, ``down [E, C, ff]``) at load; the per-expert parameters the
+    checkpoint names become views.  Few tokens (decoding) run two index-driven weight-streaming kernels; many tokens
+    are sorted by expert and run one pair of matrix products per expert that received any."""
+
+    gemv_max = 64  # token-expert pairs up to which the index-driven kernels are used
+
+    def __init__(self, width: int, ff: int, experts: int, top: int) -> None:
+        super().__init__()
+        self.E, self.top, self.ff = int(experts), int(top), int(ff)
+        self.router = _param(self.E, width)
+        self.e_up = nn.ParameterList([_param(ff, width) for _ in range(self.E)])
+        self.e_down = nn.ParameterList([_param(width, ff) for _ in range(self.E)])
+
+    def names(self) -> Dict[str, nn.Parameter]:
+        out = {"router": self.router}
+        for j in range(self.E):
+            out[f"e{j}.up"], out[f"e{j}.down"] = self.e_up[j], self.e_down[j]
+        return out
+
+    def finalize(self) -> None:
+        self.up = torch.stack([p.data for p in self.e_up]).contiguous()
+        self.down = torch.stack([p.data for p in self.e_down]).contiguous()
+        for j in range(self.E):
+            self.e_up[j].data, self.e_down[j].data = self.up[j], self.down[j]
+        self.router32 = self.router.data.float().contiguous()
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        N, top = h.size(0), self.top
+        idx, wt = H.router_topk(H.linear_f32(h, self.router32), top)
+        capturing = h.is_cuda and torch.cuda.is_current_stream_capturing()
+        if N * top <= self.gemv_max or capturing:
+            return H.moe_gemv(h, idx, wt, self.up, self.down)
+        flat = idx.view(-1).long()
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=self.E).tolist()
+        xin = H.gather_scale_rows(h, (order // top).to(torch.int32), wt.view(-1)[order].contiguous())
+        y = torch.empty(N * top, h.size(1), device=h.device, dtype=h.dtype)
+        r = 0
+        for e, c in enumerate(counts):
+            if c:
+                y[r:r + c] = H.linear(H.relu2_(H.linear(xin[r:r + c], self.up[e])), self.down[e])
+                r += c
+        where = torch.empty_like(order)
+        where[order] = torch.arange(order.numel(), device=order.device)
+        return H.combine_rows(y, where.to(torch.int32), N, top)
+
+
 class DenseFF(nn.Module):
     tensor_names = {"up": "up", "down": "down"}
 
@@ -311,12 +429,68 @@ class SandwichBlock(nn.Module):
         if ff is not None:
             self.norm2, self.norm2b = _LN(width), _LN(width)
 
-    def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
+    side = None
+
+    def norm_names(self) -> List[str]:
+        return ["norm1", "norm1b"] + (["norm2", "norm2b"] if self.mlp is not None else [])
+
+    def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype,
+                tokens: Optional[torch.Tensor] = None, side_table: Optional[torch.Tensor] = None) -> None:
         h = H.norm_rows(x, self.norm1.w, self.norm1.b, self.eps, "layer", dtype)
         H.norm_accumulate(x, self.mix(h, plan, st), self.norm1b.w, self.norm1b.b, self.eps)
         if self.mlp is not None:
             h = H.norm_rows(x, self.norm2.w, self.norm2.b, self.eps, "layer", dtype)
             H.norm_accumulate(x, self.mlp(h), self.norm2b.w, self.norm2b.b, self.eps)
+
+
+class _RMS(nn.Module):
+    def __init__(self, width: int) -> None:
+        super().__init__()
+        self.w, self.b = _param(width), None
+
+
+class TokenSide(nn.Module):
+    """A per-layer embedding of the current token, gated by the residual stream: ``y = proj (gelu_tanh(gate x) * e)``
+    with ``e`` this layer's slice of the shared side table; ``x += m * rms_norm(y) * norm``."""
+
+    def __init__(self, width: int, dim: int, col0: int) -> None:
+        super().__init__()
+        self.dim, self.col0 = dim, col0
+        self.gate, self.proj, self.norm = _param(dim, width), _param(width, dim), _param(width)
+
+    def forward(self, x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, eps: float, m: float, dtype: torch.dtype) -> None:
+        xa = x if dtype == torch.float32 else torch.empty(x.shape, device=x.device, dtype=dtype)
+        if xa is not x:
+            H.cast_into(x, xa)
+        g = H.token_side_gate(H.linear(xa, self.gate), table, tokens, self.col0)
+        H.norm_accumulate(x, H.linear(g, self.proj), self.norm, None, eps, "rms", m)
+
+
+class PreNormBlock(nn.Module):
+    """``x += m * mixer(norm1(x))``, ``x += m * ff(norm2(x))`` when the layer has a feed-forward, then the gated
+    per-layer token embedding when the model has one.  ``norm`` picks layer norm (weight and bias) or RMS norm."""
+
+    def __init__(self, width: int, mixer: nn.Module, ff: Optional[nn.Module], eps: float, norm: str, mult: float,
+                 side: Optional[TokenSide]) -> None:
+        super().__init__()
+        self.mix, self.mlp, self.eps, self.kind, self.mult, self.side = mixer, ff, eps, norm, float(mult), side
+        mk = _LN if norm == "layer" else _RMS
+        self.norm1 = mk(width)
+        if ff is not None:
+            self.norm2 = mk(width)
+
+    def norm_names(self) -> List[str]:
+        return ["norm1"] + (["norm2"] if self.mlp is not None else [])
+
+    def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype,
+                tokens: torch.Tensor, side_table: Optional[torch.Tensor]) -> None:
+        h = H.norm_rows(x, self.norm1.w, self.norm1.b, self.eps, self.kind, dtype)
+        H.norm_accumulate(x, self.mix(h, plan, st), None, None, self.eps, "none", self.mult)
+        if self.mlp is not None:
+            h = H.norm_rows(x, self.norm2.w, self.norm2.b, self.eps, self.kind, dtype)
+            H.norm_accumulate(x, self.mlp(h), None, None, self.eps, "none", self.mult)
+        if self.side is not None:
+            self.side(x, tokens, side_table, self.eps, self.mult, dtype)
 
 
 def _rank_of(tensors: Optional[Dict[str, torch.Tensor]], key: str, default: int) -> int:
@@ -343,32 +517,58 @@ class HybridLM(nn.Module):
             m, kind = spec["mixer"], spec["type"]
             if kind == "latent_attention":
                 mixer: nn.Module = LatentAttention(C, m, eps)
+            elif kind == "attention":
+                mixer = WindowAttention(C, m, eps)
             elif kind == "gla":
                 mixer = GatedLinearAttention(C, m, eps, ranks.get(f"l{i}.mix.a1", 16))
             else:
                 mixer = ChannelDelta(C, m, eps, ranks.get(f"l{i}.mix.a1", 16), ranks.get(f"l{i}.mix.g1", 16))
-            ff = DenseFF(C, spec["mlp"]["ff"]) if spec.get("mlp") else None
-            blocks.append(SandwichBlock(C, mixer, ff, eps))
+            mlp = spec.get("mlp")
+            if not mlp:
+                ff: Optional[nn.Module] = None
+            elif mlp["kind"] == "moe":
+                ff = MoEFF(C, mlp["expert"]["ff"], mlp["router"]["experts"], mlp["router"]["top"])
+            else:
+                ff = DenseFF(C, mlp["ff"])
+            if config.block == "sandwich":
+                blocks.append(SandwichBlock(C, mixer, ff, eps))
+            else:
+                sd = int(config.token_side["dim"]) if config.token_side else 0
+                side = TokenSide(C, sd, i * sd) if sd else None
+                blocks.append(PreNormBlock(C, mixer, ff, eps, config.norm, config.residual_mult, side))
         self.blocks = nn.ModuleList(blocks)
-        self.final_norm = _LN(C)
+        self.final_norm = _LN(C) if config.norm == "layer" else _RMS(C)
+        self.side_embed = _param(config.vocab, len(config.layers) * int(config.token_side["dim"])) if config.token_side else None
+        self.head_w = None if config.tied_head else _param(config.vocab, C)
         self.runs = config.layer_runs()
 
     # ---- weights -------------------------------------------------------------------------------
     def tensor_map(self) -> Dict[str, nn.Parameter]:
         """Checkpoint tensor name -> parameter."""
-        out: Dict[str, nn.Parameter] = {"embed": self.embed, "final.norm": self.final_norm.w, "final.norm.b": self.final_norm.b}
+        out: Dict[str, nn.Parameter] = {"embed": self.embed, "final.norm": self.final_norm.w}
+        if self.final_norm.b is not None:
+            out["final.norm.b"] = self.final_norm.b
         if self.loop_in is not None:
             out["loop.in"] = self.loop_in
+        if self.side_embed is not None:
+            out["side.embed"] = self.side_embed
+        if self.head_w is not None:
+            out["head"] = self.head_w
         for i, blk in enumerate(self.blocks):
-            norms = ["norm1", "norm1b"] + (["norm2", "norm2b"] if blk.mlp is not None else [])
-            for n in norms:
+            for n in blk.norm_names():
                 out[f"l{i}.{n}"] = getattr(blk, n).w
-                out[f"l{i}.{n}.b"] = getattr(blk, n).b
+                if getattr(blk, n).b is not None:
+                    out[f"l{i}.{n}.b"] = getattr(blk, n).b
             for short, attr in blk.mix.tensor_names.items():
                 out[f"l{i}.mix.{short}"] = getattr(blk.mix, attr)
-            if blk.mlp is not None:
+            if isinstance(blk.mlp, MoEFF):
+                for short, prm in blk.mlp.names().items():
+                    out[f"l{i}.mlp.{short}"] = prm
+            elif blk.mlp is not None:
                 for short, attr in blk.mlp.tensor_names.items():
                     out[f"l{i}.mlp.{short}"] = getattr(blk.mlp, attr)
+            if blk.side is not None:
+                out[f"l{i}.side.gate"], out[f"l{i}.side.proj"], out[f"l{i}.side.norm"] = blk.side.gate, blk.side.proj, blk.side.norm
         return out
 
     def load_tensors(self, tensors: Dict[str, torch.Tensor], device: Union[str, torch.device], dtype: torch.dtype) -> "HybridLM":
@@ -405,6 +605,8 @@ class HybridLM(nn.Module):
     def finalize(self) -> "HybridLM":
         for blk in self.blocks:
             blk.mix.finalize()
+            if isinstance(blk.mlp, MoEFF):
+                blk.mlp.finalize()
         self.dtype, self.device = self.embed.dtype, self.embed.device
         return self
 
@@ -435,16 +637,16 @@ class HybridLM(nn.Module):
                     x = y
                 else:
                     H.cast_into(y, x)
-            self.blocks[li](x, plan, pool.runs[run], dt)
+            self.blocks[li](x, plan, pool.runs[run], dt, tokens, self.side_embed)
             if trace is not None:
                 trace.append(x.clone())
         return x
 
     @torch.inference_mode()
     def head(self, x: torch.Tensor) -> torch.Tensor:
-        """fp32 logits of residual rows ``x [n, width]``: final norm, tied embedding, soft cap."""
-        h = H.norm_rows(x, self.final_norm.w, self.final_norm.b, self.config.norm_eps, "layer", self.dtype)
-        return H.softcap(H.linear(h, self.embed), self.config.logit_softcap)
+        """fp32 logits of residual rows ``x [n, width]``: final norm, output head (tied or its own), soft cap."""
+        h = H.norm_rows(x, self.final_norm.w, self.final_norm.b, self.config.norm_eps, self.config.norm, self.dtype)
+        return H.softcap(H.linear(h, self.embed if self.head_w is None else self.head_w), self.config.logit_softcap)
 
     def forward(self, tokens: torch.Tensor, plan: H.BatchPlan, pool: StatePool, rows: Optional[Sequence[int]] = None,
                 trace: Optional[List[torch.Tensor]] = None) -> torch.Tensor:

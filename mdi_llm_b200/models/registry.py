@@ -265,6 +265,7 @@ def lookup(name: str) -> Dict[str, Any]:
 # ``config.json["architecture"]`` -> (config class, model class), as dotted paths resolved on first use.
 architectures: Dict[str, Tuple[str, str]] = {
     "Badapel": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
+    "Vudelix": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
 }
 
 

@@ -85,14 +85,23 @@ __global__ void cast_rows_kernel(const Tin* __restrict__ in, long long in_stride
 }
 
 // kind 0: (x - mean) / sqrt(var + eps) * w + b      kind 1: x / sqrt(mean(x^2) + eps) * w
-// accumulate != 0: out (fp32) += result, the residual update of a sandwich block; else out = result.
+// kind 2: x (no normalisation).  accumulate != 0: out (fp32) += scale * result, the residual update of a block;
+// else out = result.
 template <typename Tin, typename Tw, typename Tout>
 __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride, const Tw* __restrict__ w,
                                  const Tw* __restrict__ b, Tout* __restrict__ out, long long out_stride, int n,
-                                 float eps, int kind, int accumulate) {
+                                 float eps, int kind, int accumulate, float scale) {
   __shared__ float red[33];
   const Tin* src = in + (size_t)blockIdx.x * in_stride;
   Tout* dst = out + (size_t)blockIdx.x * out_stride;
+  if (kind == 2) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float y = to_f(src[i]);
+      if (accumulate) dst[i] = from_f<Tout>(to_f(dst[i]) + scale * y);
+      else dst[i] = from_f<Tout>(y);
+    }
+    return;
+  }
   float mean = 0.f;
   if (kind == 0) {
     float s = 0.f;
@@ -109,7 +118,7 @@ __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride
     float y = (to_f(src[i]) - mean) * inv;
     if (w) y *= to_f(w[i]);
     if (b) y += to_f(b[i]);
-    if (accumulate) dst[i] = from_f<Tout>(to_f(dst[i]) + y);
+    if (accumulate) dst[i] = from_f<Tout>(to_f(dst[i]) + scale * y);
     else dst[i] = from_f<Tout>(y);
   }
 }
@@ -117,9 +126,13 @@ __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride
 // act 0: gelu(erf) in place.  act 1: out[r, c] = a[r, c] * sigmoid(g[r, c]) where a is stored head-major
 // ([heads, rows, hv]) and out/g are row-major ([rows, heads * hv]).
 template <typename T>
-__global__ void gelu_rows_kernel(T* __restrict__ x, long long total) {
+__global__ void gelu_rows_kernel(T* __restrict__ x, long long total, int act) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < total) x[i] = from_f<T>(gelu_erff_(to_f(x[i])));
+  if (i >= total) return;
+  float v = to_f(x[i]);
+  if (act == 0) v = gelu_erff_(v);
+  else { v = fmaxf(v, 0.f); v = v * v; }  // squared ReLU
+  x[i] = from_f<T>(v);
 }
 template <typename T>
 __global__ void headmajor_gate_kernel(const T* __restrict__ a, const T* __restrict__ g, long long g_stride,
@@ -318,15 +331,17 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
 // j <= first_pos + i; p = softmax(scale * s) over those, zeros elsewhere, written in the activation type.
 template <typename T>
 __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict__ p, int rows_per_head, int keys,
-                                      int first_pos, float scale) {
+                                      int first_pos, float scale, int window, int key0) {
   __shared__ float red[33];
   size_t row = blockIdx.x;
   int i = (int)(row % rows_per_head);
-  int vis = min(keys, first_pos + i + 1);
+  int pos = first_pos + i;  // column j is position key0 + j; visible: pos - window < key0 + j <= pos
+  int vis = max(0, min(keys, pos - key0 + 1));
+  int lo = window > 0 ? max(0, pos - window + 1 - key0) : 0;
   const float* src = s + row * keys;
   T* dst = p + row * keys;
   float m = -INFINITY;
-  for (int j = threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, src[j]);
+  for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, src[j]);
   m = warp_max(m);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
@@ -334,11 +349,11 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
   m = -INFINITY;
   for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
   float sum = 0.f;
-  for (int j = threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
+  for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
   sum = block_sum(sum, red);
   float inv = 1.f / sum;
   for (int j = threadIdx.x; j < keys; j += blockDim.x)
-    dst[j] = from_f<T>(j < vis ? expf((src[j] - m) * scale) * inv : 0.f);
+    dst[j] = from_f<T>(j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -737,12 +752,12 @@ int hyb_cast_rows(const void* in, long long in_stride, int in_dt, void* out, lon
 // w/b have dtype w_dt; in has in_dt; out has out_dt.  Supported (in, w, out): all fp32, or w bf16 with in/out in
 // {bf16, fp32}.
 int hyb_norm_rows(const void* in, long long in_stride, int in_dt, const void* w, const void* b, int w_dt, void* out,
-                  long long out_stride, int out_dt, int rows, int n, float eps, int kind, int accumulate,
+                  long long out_stride, int out_dt, int rows, int n, float eps, int kind, int accumulate, float scale,
                   cudaStream_t st) {
   if (rows == 0) return 0;
 #define NR(TI, TW, TO)                                                                                              \
   norm_rows_kernel<TI, TW, TO><<<rows, 256, 0, st>>>((const TI*)in, in_stride, (const TW*)w, (const TW*)b, (TO*)out, \
-                                                      out_stride, n, eps, kind, accumulate)
+                                                      out_stride, n, eps, kind, accumulate, scale)
   if (w_dt == 1) {
     if (in_dt != 1 || out_dt != 1) return -3;
     NR(float, float, float);
@@ -754,11 +769,11 @@ int hyb_norm_rows(const void* in, long long in_stride, int in_dt, const void* w,
   return (int)cudaGetLastError();
 }
 
-int hyb_gelu_rows(void* x, long long total, int dt, cudaStream_t st) {
+int hyb_gelu_rows(void* x, long long total, int dt, int act, cudaStream_t st) {
   if (total == 0) return 0;
   int blocks = (int)((total + 255) / 256);
-  HYB_DISPATCH(dt, (gelu_rows_kernel<bf16><<<blocks, 256, 0, st>>>((bf16*)x, total)),
-               (gelu_rows_kernel<float><<<blocks, 256, 0, st>>>((float*)x, total)));
+  HYB_DISPATCH(dt, (gelu_rows_kernel<bf16><<<blocks, 256, 0, st>>>((bf16*)x, total, act)),
+               (gelu_rows_kernel<float><<<blocks, 256, 0, st>>>((float*)x, total, act)));
   return (int)cudaGetLastError();
 }
 
@@ -825,11 +840,11 @@ int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const v
 }
 
 int hyb_causal_softmax(const float* s, void* p, long long rows, int rows_per_head, int keys, int first_pos, float scale,
-                       int dt, cudaStream_t st) {
+                       int window, int key0, int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   if (scale <= 0.f) return -3;  // the row maximum is taken before scaling
-  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale)),
-               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale)));
+  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0)),
+               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0)));
   return (int)cudaGetLastError();
 }
 
@@ -934,5 +949,381 @@ int hyb_gated_recurrence(const RecArgs* args, int nseq, int N, int dt, int varia
 const char* hyb_build_digest() { return "MDI_BUILD_DIGEST:" MDI_BUILD_DIGEST_STR; }
 
 const char* hyb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
+
+}  // extern "C"
+
+// =========================================================================================================
+// windowed grouped-query attention, per-layer token embedding gate, mixture of experts
+// =========================================================================================================
+namespace hyb {
+
+__device__ __forceinline__ float gelu_tanhf_(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// One block per token.  Warps walk the H query heads and then the G key heads: rotate the first `nrot` entries
+// (entry 2i with 2i+1, angle pos * inv_freq[i]), divide the head by its root mean square over D, store queries
+// in place and keys into the slot's cache row; the values are copied behind the keys.  D <= 256.
+#define WA_MAXD 8
+template <typename T>
+__global__ void window_append_kernel(T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
+                                     const T* __restrict__ v, long long v_stride, const float* __restrict__ inv_freq,
+                                     T* __restrict__ cache, long long slot_stride, const int* __restrict__ meta,
+                                     const int* __restrict__ tok_seq, int H, int G, int D, int V, int nrot, float eps) {
+  int t = blockIdx.x;
+  const int* m = meta + 4 * tok_seq[t];
+  int pos = m[3] + (t - m[0]);
+  T* row = cache + (size_t)m[2] * slot_stride + (size_t)pos * (G * (D + V));
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float fpos = (float)pos;
+  for (int hv = w; hv < H + G; hv += nw) {
+    const T* src = hv < H ? q + (size_t)t * q_stride + (size_t)hv * D : k + (size_t)t * k_stride + (size_t)(hv - H) * D;
+    T* dst = hv < H ? q + (size_t)t * q_stride + (size_t)hv * D : row + (size_t)(hv - H) * D;
+    float y[WA_MAXD];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < WA_MAXD; ++c) {
+      int d = lane + 32 * c;
+      y[c] = 0.f;
+      if (d < D) {
+        float x = to_f(src[d]);
+        if (d < nrot) {
+          float o = to_f(src[d ^ 1]), sn, cs;
+          sincosf(fpos * inv_freq[d >> 1], &sn, &cs);
+          x = (d & 1) ? x * cs + o * sn : x * cs - o * sn;
+        }
+        y[c] = x;
+        ss += x * x;
+      }
+    }
+    ss = warp_sum(ss);  // also orders every lane's loads before the in-place stores below
+    float inv = 1.f / sqrtf(ss / D + eps);
+#pragma unroll
+    for (int c = 0; c < WA_MAXD; ++c) {
+      int d = lane + 32 * c;
+      if (d < D) dst[d] = from_f<T>(y[c] * inv);
+    }
+  }
+  const T* vs = v + (size_t)t * v_stride;
+  T* vd = row + (size_t)G * D;
+  for (int i = threadIdx.x; i < G * V; i += blockDim.x) vd[i] = vs[i];
+}
+
+// One block per (token, key/value head); warp w is query head g * rep + w.  A tile of 32 cached keys and values is
+// staged in shared memory as fp32 once and used by all heads of the group; lane j scores key j, the online softmax
+// and the weighted sum are fp32; the result is multiplied by sigmoid(gate) per head.  V <= 256.
+#define WT_TILE 32
+#define WT_MAXV 8
+template <typename T>
+__global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ gate,
+                                   long long g_stride, const T* __restrict__ cache, long long slot_stride,
+                                   const int* __restrict__ meta, const int* __restrict__ tok_seq, T* __restrict__ out,
+                                   int H, int G, int D, int V, float scale, int window) {
+  extern __shared__ float sm[];
+  int rep = H / G;
+  float* qs = sm;                       // [rep][D]
+  float* Kt = qs + rep * D;             // [32][D + 1]
+  float* Vt = Kt + WT_TILE * (D + 1);   // [32][V]
+  int t = blockIdx.x, g = blockIdx.y;
+  const int* m = meta + 4 * tok_seq[t];
+  int pos = m[3] + (t - m[0]);
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const T* base = cache + (size_t)m[2] * slot_stride;
+  int rowlen = G * (D + V);
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < rep * D; i += blockDim.x)
+    qs[i] = to_f(q[(size_t)t * q_stride + (size_t)g * rep * D + i]);
+  float acc[WT_MAXV];
+#pragma unroll
+  for (int c = 0; c < WT_MAXV; ++c) acc[c] = 0.f;
+  float mx = -INFINITY, l = 0.f;
+  for (int j0 = lo; j0 <= pos; j0 += WT_TILE) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < WT_TILE * D; i += blockDim.x) {
+      int j = i / D, d = i - j * D;
+      Kt[j * (D + 1) + d] = j0 + j <= pos ? to_f(base[(size_t)(j0 + j) * rowlen + g * D + d]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < WT_TILE * V; i += blockDim.x) {
+      int j = i / V, d = i - j * V;
+      Vt[i] = j0 + j <= pos ? to_f(base[(size_t)(j0 + j) * rowlen + G * D + g * V + d]) : 0.f;
+    }
+    __syncthreads();
+    float s = -INFINITY;
+    if (j0 + lane <= pos) {
+      const float* qr = qs + w * D;
+      const float* kr = Kt + lane * (D + 1);
+      float a = 0.f;
+      for (int d = 0; d < D; ++d) a += qr[d] * kr[d];
+      s = a * scale;
+    }
+    float mn = fmaxf(mx, warp_max(s));
+    float pj = j0 + lane <= pos ? expf(s - mn) : 0.f;
+    float corr = expf(mx - mn);  // first tile: exp(-inf) = 0
+    l = l * corr + warp_sum(pj);
+    mx = mn;
+#pragma unroll
+    for (int c = 0; c < WT_MAXV; ++c) acc[c] *= corr;
+    for (int j = 0; j < WT_TILE; ++j) {
+      float pv = __shfl_sync(0xffffffffu, pj, j);
+#pragma unroll
+      for (int c = 0; c < WT_MAXV; ++c) {
+        int d = lane + 32 * c;
+        if (d < V) acc[c] += pv * Vt[j * V + d];
+      }
+    }
+  }
+  int h = g * rep + w;
+  float gt = gate ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
+  float inv = gt / l;
+#pragma unroll
+  for (int c = 0; c < WT_MAXV; ++c) {
+    int d = lane + 32 * c;
+    if (d < V) out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(acc[c] * inv);
+  }
+}
+
+// out[r, h*hv + d] = a[h, r, d] * sigmoid(g[r, h]): one gate per head, a stored head-major.
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ a, const T* __restrict__ g, long long g_stride,
+                                 T* __restrict__ out, int rows, int heads, int hv) {
+  int r = blockIdx.x;
+  int n = heads * hv;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    int h = c / hv, d = c - h * hv;
+    float v = to_f(a[((size_t)h * rows + r) * hv + d]);
+    out[(size_t)r * n + c] = from_f<T>(v * sigmoidf_(to_f(g[(size_t)r * g_stride + h])));
+  }
+}
+
+// out[r, c] = gelu_tanh(z[r, c]) * table[tokens[r], col0 + c]
+template <typename T>
+__global__ void token_side_gate_kernel(const T* __restrict__ z, long long z_stride, const T* __restrict__ table,
+                                       long long t_stride, int col0, const int* __restrict__ tokens,
+                                       T* __restrict__ out, int d) {
+  int r = blockIdx.x;
+  const T* e = table + (size_t)tokens[r] * t_stride + col0;
+  for (int c = threadIdx.x; c < d; c += blockDim.x)
+    out[(size_t)r * d + c] = from_f<T>(gelu_tanhf_(to_f(z[(size_t)r * z_stride + c])) * to_f(e[c]));
+}
+
+// One thread per token: the `top` largest logits (ties to the lower index), scores = sigmoid(logit).
+__global__ void router_topk_kernel(const float* __restrict__ z, int* __restrict__ idx, float* __restrict__ wt, int N,
+                                   int E, int top) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= N) return;
+  const float* row = z + (size_t)t * E;
+  for (int k = 0; k < top; ++k) {
+    int best = -1;
+    float bv = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= idx[(size_t)t * top + j] == e;
+      float v = row[e];
+      if (!taken && (best < 0 || v > bv)) { best = e; bv = v; }
+    }
+    idx[(size_t)t * top + k] = best;
+    wt[(size_t)t * top + k] = sigmoidf_(bv);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const T* __restrict__ wrow, const float* __restrict__ xs, int n, int lane) {
+  float a = 0.f;
+  if ((n & 7) == 0) {
+    for (int c = lane * 8; c < n; c += 256) {
+      float f[8];
+      load8(wrow + c, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a += f[i] * xs[c + i];
+    }
+  } else {
+    for (int c = lane; c < n; c += 32) a += to_f(wrow[c]) * xs[c];
+  }
+  return warp_sum(a);
+}
+
+// act[p, f] = relu(up[e_p][f, :] . (w_p * h[t_p, :]))^2 for pair p = (token, slot k); grid (pairs, ceil(ff / 32)).
+#define MOE_ROWS 32
+template <typename T>
+__global__ void moe_up_kernel(const T* __restrict__ h, long long h_stride, const int* __restrict__ idx,
+                              const float* __restrict__ wt, const T* __restrict__ up, float* __restrict__ act, int top,
+                              int C, int ff) {
+  extern __shared__ float sm[];
+  int p = blockIdx.x, t = p / top;
+  int e = idx[p];
+  float w = wt[p];
+  for (int c = threadIdx.x; c < C; c += blockDim.x) sm[c] = to_f(from_f<T>(w * to_f(h[(size_t)t * h_stride + c])));
+  __syncthreads();
+  int lane = threadIdx.x & 31, wp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const T* we = up + (size_t)e * ff * C;
+  for (int r = wp; r < MOE_ROWS; r += nw) {
+    int f = blockIdx.y * MOE_ROWS + r;
+    if (f >= ff) break;
+    float a = dot_row(we + (size_t)f * C, sm, C, lane);
+    if (lane == 0) { a = fmaxf(a, 0.f); act[(size_t)p * ff + f] = a * a; }
+  }
+}
+
+// out[t, c] = sum_k down[e_(t,k)][c, :] . act[(t,k), :]; grid (tokens, ceil(C / 32)).
+template <typename T>
+__global__ void moe_down_kernel(const float* __restrict__ act, const int* __restrict__ idx, const T* __restrict__ down,
+                                T* __restrict__ out, int top, int C, int ff) {
+  extern __shared__ float sm[];
+  int t = blockIdx.x;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) sm[i] = act[(size_t)t * top * ff + i];
+  __syncthreads();
+  int lane = threadIdx.x & 31, wp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int r = wp; r < MOE_ROWS; r += nw) {
+    int c = blockIdx.y * MOE_ROWS + r;
+    if (c >= C) break;
+    float a = 0.f;
+    for (int k = 0; k < top; ++k)
+      a += dot_row(down + ((size_t)idx[(size_t)t * top + k] * C + c) * ff, sm + k * ff, ff, lane);
+    if (lane == 0) out[(size_t)t * C + c] = from_f<T>(a);
+  }
+}
+
+template <typename T>
+__global__ void gather_scale_rows_kernel(const T* __restrict__ h, long long h_stride, const int* __restrict__ rows,
+                                         const float* __restrict__ scale, T* __restrict__ out, int C) {
+  int i = blockIdx.x;
+  const T* src = h + (size_t)rows[i] * h_stride;
+  float w = scale[i];
+  for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)i * C + c] = from_f<T>(w * to_f(src[c]));
+}
+
+template <typename T>
+__global__ void combine_rows_kernel(const T* __restrict__ y, const int* __restrict__ where, T* __restrict__ out, int top,
+                                    int C) {
+  int t = blockIdx.x;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a += to_f(y[(size_t)where[(size_t)t * top + k] * C + c]);
+    out[(size_t)t * C + c] = from_f<T>(a);
+  }
+}
+
+}  // namespace hyb
+
+extern "C" {
+
+int hyb_window_append(void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                      const float* inv_freq, void* cache, long long slot_stride, const int* meta, const int* tok_seq,
+                      int N, int H, int G, int D, int V, int nrot, float eps, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  if (D > 32 * WA_MAXD || nrot > D || (nrot & 1) || (nrot > 0 && !inv_freq)) return -3;
+  HYB_DISPATCH(dt,
+               (window_append_kernel<bf16><<<N, 128, 0, st>>>((bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
+                                                              v_stride, inv_freq, (bf16*)cache, slot_stride, meta, tok_seq,
+                                                              H, G, D, V, nrot, eps)),
+               (window_append_kernel<float><<<N, 128, 0, st>>>((float*)q, q_stride, (const float*)k, k_stride,
+                                                               (const float*)v, v_stride, inv_freq, (float*)cache,
+                                                               slot_stride, meta, tok_seq, H, G, D, V, nrot, eps)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_window_attn(const void* q, long long q_stride, const void* gate, long long g_stride, const void* cache,
+                    long long slot_stride, const int* meta, const int* tok_seq, void* out, int N, int H, int G, int D,
+                    int V, float scale, int window, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  int rep = G > 0 ? H / G : 0;
+  if (rep < 1 || rep * G != H || rep > 32 || V > 32 * WT_MAXV) return -3;
+  size_t smem = ((size_t)rep * D + (size_t)WT_TILE * (D + 1) + (size_t)WT_TILE * V) * sizeof(float);
+  if (smem > 220 * 1024) return -3;
+  dim3 grid(N, G);
+  cudaError_t e;
+  if (dt == 0) {
+    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    window_attn_kernel<bf16><<<grid, 32 * rep, smem, st>>>((const bf16*)q, q_stride, (const bf16*)gate, g_stride,
+                                                           (const bf16*)cache, slot_stride, meta, tok_seq, (bf16*)out, H,
+                                                           G, D, V, scale, window);
+  } else {
+    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    window_attn_kernel<float><<<grid, 32 * rep, smem, st>>>((const float*)q, q_stride, (const float*)gate, g_stride,
+                                                            (const float*)cache, slot_stride, meta, tok_seq, (float*)out,
+                                                            H, G, D, V, scale, window);
+  }
+  return (int)cudaGetLastError();
+}
+
+int hyb_head_gate(const void* a, const void* g, long long g_stride, void* out, int rows, int heads, int hv, int dt,
+                  cudaStream_t st) {
+  if (rows == 0) return 0;
+  HYB_DISPATCH(dt,
+               (head_gate_kernel<bf16><<<rows, 256, 0, st>>>((const bf16*)a, (const bf16*)g, g_stride, (bf16*)out, rows,
+                                                             heads, hv)),
+               (head_gate_kernel<float><<<rows, 256, 0, st>>>((const float*)a, (const float*)g, g_stride, (float*)out,
+                                                              rows, heads, hv)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_token_side_gate(const void* z, long long z_stride, const void* table, long long t_stride, int col0,
+                        const int* tokens, void* out, int N, int d, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  int th = d >= 256 ? 256 : (d >= 64 ? 64 : 32);
+  HYB_DISPATCH(dt,
+               (token_side_gate_kernel<bf16><<<N, th, 0, st>>>((const bf16*)z, z_stride, (const bf16*)table, t_stride,
+                                                               col0, tokens, (bf16*)out, d)),
+               (token_side_gate_kernel<float><<<N, th, 0, st>>>((const float*)z, z_stride, (const float*)table, t_stride,
+                                                                col0, tokens, (float*)out, d)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, cudaStream_t st) {
+  if (N == 0) return 0;
+  if (top < 1 || top > E) return -3;
+  router_topk_kernel<<<(N + 63) / 64, 64, 0, st>>>(z, idx, wt, N, E, top);
+  return (int)cudaGetLastError();
+}
+
+int hyb_moe_up(const void* h, long long h_stride, const int* idx, const float* wt, const void* up, float* act, int N,
+               int top, int C, int ff, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  size_t smem = (size_t)C * sizeof(float);
+  if (smem > 200 * 1024) return -3;
+  dim3 grid(N * top, (ff + MOE_ROWS - 1) / MOE_ROWS);
+  cudaError_t e;
+  if (dt == 0) {
+    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    moe_up_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)h, h_stride, idx, wt, (const bf16*)up, act, top, C, ff);
+  } else {
+    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    moe_up_kernel<float><<<grid, 256, smem, st>>>((const float*)h, h_stride, idx, wt, (const float*)up, act, top, C, ff);
+  }
+  return (int)cudaGetLastError();
+}
+
+int hyb_moe_down(const float* act, const int* idx, const void* down, void* out, int N, int top, int C, int ff, int dt,
+                 cudaStream_t st) {
+  if (N == 0) return 0;
+  size_t smem = (size_t)top * ff * sizeof(float);
+  if (smem > 200 * 1024) return -3;
+  dim3 grid(N, (C + MOE_ROWS - 1) / MOE_ROWS);
+  cudaError_t e;
+  if (dt == 0) {
+    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    moe_down_kernel<bf16><<<grid, 256, smem, st>>>(act, idx, (const bf16*)down, (bf16*)out, top, C, ff);
+  } else {
+    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    moe_down_kernel<float><<<grid, 256, smem, st>>>(act, idx, (const float*)down, (float*)out, top, C, ff);
+  }
+  return (int)cudaGetLastError();
+}
+
+int hyb_gather_scale_rows(const void* h, long long h_stride, const int* rows, const float* scale, void* out, int M, int C,
+                          int dt, cudaStream_t st) {
+  if (M == 0) return 0;
+  HYB_DISPATCH(dt,
+               (gather_scale_rows_kernel<bf16><<<M, 256, 0, st>>>((const bf16*)h, h_stride, rows, scale, (bf16*)out, C)),
+               (gather_scale_rows_kernel<float><<<M, 256, 0, st>>>((const float*)h, h_stride, rows, scale, (float*)out, C)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_combine_rows(const void* y, const int* where, void* out, int n, int top, int C, int dt, cudaStream_t st) {
+  if (n == 0) return 0;
+  HYB_DISPATCH(dt, (combine_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)y, where, (bf16*)out, top, C)),
+               (combine_rows_kernel<float><<<n, 256, 0, st>>>((const float*)y, where, (float*)out, top, C)));
+  return (int)cudaGetLastError();
+}
 
 }  // extern "C"

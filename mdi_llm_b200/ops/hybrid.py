@@ -28,7 +28,8 @@ from . import build as _build
 
 __all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
            "headmajor_gate", "softcap", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
-           "rotary_inv_freq"]
+           "rotary_inv_freq", "scaled_inv_freq", "linear_f32", "window_append", "window_attn", "head_gate", "relu2_",
+           "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows"]
 
 
 class HybridOpsError(RuntimeError):
@@ -60,13 +61,22 @@ def lib() -> ctypes.CDLL:
     h.hyb_error_string.argtypes = [i32]
     h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     h.hyb_cast_rows.argtypes = [vp, i64, i32, vp, i64, i32, i32, i32, vp]
-    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, vp]
-    h.hyb_gelu_rows.argtypes = [vp, i64, i32, vp]
+    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, vp]
+    h.hyb_gelu_rows.argtypes = [vp, i64, i32, i32, vp]
+    h.hyb_window_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
+    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp]
+    h.hyb_head_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
+    h.hyb_token_side_gate.argtypes = [vp, i64, vp, i64, i32, vp, vp, i32, i32, i32, vp]
+    h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    h.hyb_gather_scale_rows.argtypes = [vp, i64, vp, vp, vp, i32, i32, i32, vp]
+    h.hyb_combine_rows.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
     h.hyb_headmajor_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
     h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
-    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, vp]
+    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
     h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, i32, vp, vp, vp, vp]
     _lib = h
@@ -133,6 +143,29 @@ def rotary_inv_freq(dims: int, base: float, device: torch.device) -> torch.Tenso
 # ---------------------------------------------------------------------------------------------------------
 # matrix products (vendor GEMM on both devices; fp32 means fp32: TF32 is switched off for the call)
 # ---------------------------------------------------------------------------------------------------------
+def scaled_inv_freq(dims: int, base: float, scaling: Optional[dict], device: torch.device) -> torch.Tensor:
+    """Rotary frequencies with the wavelength-dependent stretch used for context extension: with ``l = 2 pi / f``,
+    ``f`` is kept for ``l < original/high``, divided by ``factor`` for ``l > original/low``, and blended linearly in
+    ``s = (original/l - low) / (high - low)`` between the two.  float64, rounded once to fp32."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    if scaling:
+        factor, low, high = float(scaling["factor"]), float(scaling["low"]), float(scaling["high"])
+        orig = float(scaling["original"])
+        wl = 2.0 * math.pi / f
+        s = (orig / wl - low) / (high - low) if high != low else torch.ones_like(f)
+        mid = (1.0 - s) * f / factor + s * f
+        f = torch.where(wl < orig / high, f, torch.where(wl > orig / low, f / factor, mid))
+    return f.to(torch.float32).to(device)
+
+
+def linear_f32(x: torch.Tensor, w32: torch.Tensor) -> torch.Tensor:
+    """``x @ w32.T`` in fp32 (routers): the input may be the activation type, the product and the result are fp32."""
+    if x.is_cuda and torch.backends.cuda.matmul.allow_tf32:
+        raise HybridOpsError("TF32 matrix products are on; router logits are fp32")
+    return F.linear(x.float(), w32)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` in the activation type with fp32 accumulation."""
     if x.is_cuda and x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
@@ -166,6 +199,8 @@ def cast_into(src: torch.Tensor, dst: torch.Tensor) -> None:
 
 def _norm_torch(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, kind: str) -> torch.Tensor:
     xf = x.float()
+    if kind == "none":
+        return xf
     if kind == "layer":
         xf = xf - xf.mean(-1, keepdim=True)
     y = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
@@ -186,22 +221,27 @@ def norm_rows(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tens
     ref = w if w is not None else x
     _check(lib().hyb_norm_rows(x.data_ptr(), xs, _dt(x), None if w is None else w.data_ptr(),
                                None if b is None else b.data_ptr(), _dt(ref), out.data_ptr(), n, _dt(out), x.size(0), n,
-                               eps, 0 if kind == "layer" else 1, 0, _st()), "norm_rows")
+                               eps, _NORM_KINDS[kind], 0, 1.0, _st()), "norm_rows")
     return out
 
 
-def norm_accumulate(resid: torch.Tensor, y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float,
-                    kind: str = "layer") -> None:
-    """``resid += norm(y)``: the post-norm and the residual sum of a sandwich block in one pass (fp32 residual)."""
+_NORM_KINDS = {"layer": 0, "rms": 1, "none": 2}
+
+
+def norm_accumulate(resid: torch.Tensor, y: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float,
+                    kind: str = "layer", scale: float = 1.0) -> None:
+    """``resid += scale * norm(y)`` in one pass over the fp32 residual: the post-norm and residual sum of a sandwich
+    block (``kind`` "layer" or "rms"), or the scaled residual sum of a pre-norm block (``kind="none"``: no norm)."""
     if resid.dtype != torch.float32:
         raise HybridOpsError("the residual stream is fp32")
     if not y.is_cuda:
-        resid.add_(_norm_torch(y, w, b, eps, kind))
+        resid.add_(_norm_torch(y, w, b, eps, kind), alpha=float(scale))
         return
     ys, n = _rows(y)
-    _check(lib().hyb_norm_rows(y.data_ptr(), ys, _dt(y), w.data_ptr(), None if b is None else b.data_ptr(), _dt(w),
-                               resid.data_ptr(), resid.stride(0), 1, y.size(0), n, eps, 0 if kind == "layer" else 1, 1,
-                               _st()), "norm_accumulate")
+    ref = w if w is not None else y
+    _check(lib().hyb_norm_rows(y.data_ptr(), ys, _dt(y), None if w is None else w.data_ptr(),
+                               None if b is None else b.data_ptr(), _dt(ref), resid.data_ptr(), resid.stride(0), 1,
+                               y.size(0), n, eps, _NORM_KINDS[kind], 1, float(scale), _st()), "norm_accumulate")
 
 
 def gelu_(x: torch.Tensor) -> torch.Tensor:
@@ -209,8 +249,42 @@ def gelu_(x: torch.Tensor) -> torch.Tensor:
     if not x.is_cuda:
         return x.copy_(F.gelu(x.float()).to(x.dtype))
     assert x.is_contiguous()
-    _check(lib().hyb_gelu_rows(x.data_ptr(), x.numel(), _dt(x), _st()), "gelu")
+    _check(lib().hyb_gelu_rows(x.data_ptr(), x.numel(), _dt(x), 0, _st()), "gelu")
     return x
+
+
+def relu2_(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0)^2`` in place on a dense tensor."""
+    if not x.is_cuda:
+        return x.copy_(torch.relu(x.float()).square().to(x.dtype))
+    assert x.is_contiguous()
+    _check(lib().hyb_gelu_rows(x.data_ptr(), x.numel(), _dt(x), 1, _st()), "relu2")
+    return x
+
+
+def head_gate(a: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """``a [heads, rows, hv]`` (head-major) times ``sigmoid(g [rows, heads])``, one gate per head -> ``[rows, heads*hv]``."""
+    H, N, hv = a.shape
+    if not a.is_cuda:
+        return (a.permute(1, 0, 2).float() * torch.sigmoid(g.float())[:, :, None]).reshape(N, H * hv).to(a.dtype)
+    assert a.is_contiguous()
+    gs, _ = _rows(g)
+    out = torch.empty(N, H * hv, device=a.device, dtype=a.dtype)
+    _check(lib().hyb_head_gate(a.data_ptr(), g.data_ptr(), gs, out.data_ptr(), N, H, hv, _dt(a), _st()), "head_gate")
+    return out
+
+
+def token_side_gate(z: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, col0: int) -> torch.Tensor:
+    """``gelu_tanh(z [N, d]) * table[tokens, col0:col0+d]``: the gate of a per-layer token embedding."""
+    N, d = z.shape
+    if not z.is_cuda:
+        e = table[tokens.long(), col0:col0 + d].float()
+        return (F.gelu(z.float(), approximate="tanh") * e).to(z.dtype)
+    zs, _ = _rows(z)
+    out = torch.empty(N, d, device=z.device, dtype=z.dtype)
+    _check(lib().hyb_token_side_gate(z.data_ptr(), zs, table.data_ptr(), table.stride(0), int(col0), tokens.data_ptr(),
+                                     out.data_ptr(), N, d, _dt(z), _st()), "token_side_gate")
+    return out
 
 
 def headmajor_gate(a: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
@@ -311,20 +385,159 @@ def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: 
     return out
 
 
-def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """``softmax(scale * scores)`` over the visible keys of fp32 ``scores [heads, rows, keys]``: row ``i`` sees keys
-    ``j <= first_pos + i``; hidden keys get probability 0.  Result in ``out_dtype``."""
+def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype: torch.dtype, window: int = 0,
+                   key0: int = 0) -> torch.Tensor:
+    """``softmax(scale * scores)`` over the visible keys of fp32 ``scores [heads, rows, keys]``: row ``i`` is position
+    ``first_pos + i``, column ``j`` is position ``key0 + j``; a key is visible when it is not later than the row and,
+    with ``window > 0``, fewer than ``window`` positions back.  Hidden keys get probability 0.  Result in ``out_dtype``."""
     Hh, n, keys = scores.shape
     if not scores.is_cuda:
-        j = torch.arange(keys)
-        hidden = j[None, None, :] > (first_pos + torch.arange(n))[None, :, None]
+        j = key0 + torch.arange(keys)
+        pi = (first_pos + torch.arange(n))[None, :, None]
+        hidden = j[None, None, :] > pi
+        if window > 0:
+            hidden = hidden | (pi - j[None, None, :] >= window)
         return torch.softmax((scores.float() * scale).masked_fill(hidden, float("-inf")), -1).to(out_dtype)
     if scores.dtype != torch.float32 or not scores.is_contiguous():
         raise HybridOpsError("scores are dense fp32")
     p = torch.empty(Hh, n, keys, device=scores.device, dtype=out_dtype)
-    _check(lib().hyb_causal_softmax(scores.data_ptr(), p.data_ptr(), Hh * n, n, keys, int(first_pos), float(scale), _dt(p), _st()),
-           "causal_softmax")
+    _check(lib().hyb_causal_softmax(scores.data_ptr(), p.data_ptr(), Hh * n, n, keys, int(first_pos), float(scale),
+                                    int(window), int(key0), _dt(p), _st()), "causal_softmax")
     return p
+
+
+# ---------------------------------------------------------------------------------------------------------
+# windowed grouped-query attention with a per-slot key/value cache
+# ---------------------------------------------------------------------------------------------------------
+def window_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: Optional[torch.Tensor], cache: torch.Tensor,
+                  plan: BatchPlan, H: int, G: int, D: int, V: int, nrot: int, eps: float) -> None:
+    """Per token: rotate the first ``nrot`` entries of every query and key head (entry ``2i`` paired with ``2i+1``,
+    angle ``pos * inv_freq[i]``), divide each head by its root mean square over ``D`` (``eps`` inside the root), keep
+    the queries in place and write ``[keys | values]`` to ``cache[slot, pos]`` (row = ``G*D`` keys then ``G*V`` values)."""
+    if not q.is_cuda:
+        N = q.size(0)
+
+        def prep(x: torch.Tensor, heads: int) -> torch.Tensor:
+            xf = x.float().reshape(N, heads, D).clone()
+            if nrot:
+                ang = plan.positions.float()[:, None] * inv_freq[None, :]
+                c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                u, w_ = xf[..., 0:nrot:2].clone(), xf[..., 1:nrot:2].clone()
+                xf[..., 0:nrot:2] = u * c - w_ * s_
+                xf[..., 1:nrot:2] = w_ * c + u * s_
+            xf = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
+            return xf.reshape(N, heads * D).to(x.dtype)
+
+        q.copy_(prep(q, H))
+        kk = prep(k, G)
+        for r0, n, slot, p0 in plan.seqs:
+            cache[slot, p0:p0 + n, :G * D] = kk[r0:r0 + n]
+            cache[slot, p0:p0 + n, G * D:] = v[r0:r0 + n]
+        return
+    _check(lib().hyb_window_append(q.data_ptr(), _rows(q)[0], k.data_ptr(), _rows(k)[0], v.data_ptr(), _rows(v)[0],
+                                   None if inv_freq is None else inv_freq.data_ptr(), cache.data_ptr(), cache.stride(0),
+                                   plan.meta.data_ptr(), plan.tok_seq.data_ptr(), q.size(0), H, G, D, V, int(nrot),
+                                   float(eps), _dt(q), _st()), "window_append")
+
+
+def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor, plan: BatchPlan, H: int, G: int, D: int,
+                V: int, scale: float, window: int) -> torch.Tensor:
+    """Softmax attention of every token over the cached keys of its slot that are not later than it and (``window > 0``)
+    fewer than ``window`` positions back; query head ``h`` reads key/value head ``h // (H/G)``.  Each head's output is
+    multiplied by ``sigmoid(g[token, h])`` when ``g`` is given.  Returns ``[N, H*V]``.  The form for one-token steps and
+    short portions: one block per token and key/value head, the cache tile shared by the group's query heads."""
+    N = q.size(0)
+    if not q.is_cuda:
+        out = torch.empty(N, H * V, dtype=q.dtype)
+        rep = H // G
+        for r0, n, slot, p0 in plan.seqs:
+            rows = cache[slot, :p0 + n].float()
+            kk = rows[:, :G * D].reshape(-1, G, D).repeat_interleave(rep, 1)  # [keys, H, D]
+            vv = rows[:, G * D:].reshape(-1, G, V).repeat_interleave(rep, 1)
+            qq = q[r0:r0 + n].float().reshape(n, H, D)
+            s = torch.einsum("nhd,khd->hnk", qq, kk) * scale
+            pi = (p0 + torch.arange(n))[None, :, None]
+            j = torch.arange(p0 + n)[None, None, :]
+            hid = j > pi
+            if window > 0:
+                hid = hid | (pi - j >= window)
+            o = torch.einsum("hnk,khv->nhv", torch.softmax(s.masked_fill(hid, float("-inf")), -1), vv)
+            if g is not None:
+                o = o * torch.sigmoid(g[r0:r0 + n].float())[:, :, None]
+            out[r0:r0 + n] = o.reshape(n, H * V).to(q.dtype)
+        return out
+    out = torch.empty(N, H * V, device=q.device, dtype=q.dtype)
+    _check(lib().hyb_window_attn(q.data_ptr(), _rows(q)[0], None if g is None else g.data_ptr(),
+                                 0 if g is None else _rows(g)[0], cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
+                                 plan.tok_seq.data_ptr(), out.data_ptr(), N, H, G, D, V, float(scale), int(window),
+                                 _dt(q), _st()), "window_attn")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# mixture of experts: sigmoid router, top-k choice, experts applied to the weighted input
+# ---------------------------------------------------------------------------------------------------------
+def router_topk(z: torch.Tensor, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """From fp32 router logits ``z [N, E]``: the ``top`` experts with the largest ``sigmoid(z)`` per token (ties go to
+    the lower index) as int32 ``[N, top]`` and their scores as fp32 ``[N, top]`` (not renormalised)."""
+    N, E = z.shape
+    if not z.is_cuda:
+        s = torch.sigmoid(z.float())
+        idx = torch.argsort(-s, dim=-1, stable=True)[:, :top]
+        return idx.to(torch.int32), torch.gather(s, 1, idx)
+    if z.dtype != torch.float32 or not z.is_contiguous():
+        raise HybridOpsError("router logits are dense fp32")
+    idx = torch.empty(N, top, device=z.device, dtype=torch.int32)
+    wt = torch.empty(N, top, device=z.device, dtype=torch.float32)
+    _check(lib().hyb_router_topk(z.data_ptr(), idx.data_ptr(), wt.data_ptr(), N, E, int(top), _st()), "router_topk")
+    return idx, wt
+
+
+def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+    """``sum_k down[e_k] relu(up[e_k] (w_k h))^2`` per token, experts read by index (``up [E, ff, C]``, ``down [E, C, ff]``).
+    The form for few tokens: two weight-streaming kernels, no grouping and no host synchronisation."""
+    N, C = h.shape
+    E, ff, _ = up.shape
+    top = idx.size(1)
+    if not h.is_cuda:
+        out = torch.zeros(N, C)
+        for t in range(N):
+            for k in range(top):
+                e = int(idx[t, k])
+                xin = (wt[t, k] * h[t].float()).to(h.dtype)
+                a = torch.relu(F.linear(xin, up[e]).float()).square().to(h.dtype)
+                out[t] += F.linear(a, down[e]).float()
+        return out.to(h.dtype)
+    assert up.is_contiguous() and down.is_contiguous() and idx.is_contiguous() and wt.is_contiguous()
+    act = torch.empty(N, top, ff, device=h.device, dtype=torch.float32)
+    out = torch.empty(N, C, device=h.device, dtype=h.dtype)
+    _check(lib().hyb_moe_up(h.data_ptr(), _rows(h)[0], idx.data_ptr(), wt.data_ptr(), up.data_ptr(), act.data_ptr(), N, top,
+                            C, ff, _dt(h), _st()), "moe_up")
+    _check(lib().hyb_moe_down(act.data_ptr(), idx.data_ptr(), down.data_ptr(), out.data_ptr(), N, top, C, ff, _dt(h), _st()),
+           "moe_down")
+    return out
+
+
+def gather_scale_rows(h: torch.Tensor, rows: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """``out[i] = scale[i] * h[rows[i]]`` (int32 ``rows``, fp32 ``scale``), rounded to the activation type."""
+    if not h.is_cuda:
+        return (h[rows.long()].float() * scale.float()[:, None]).to(h.dtype)
+    M = rows.numel()
+    out = torch.empty(M, h.size(1), device=h.device, dtype=h.dtype)
+    _check(lib().hyb_gather_scale_rows(h.data_ptr(), _rows(h)[0], rows.data_ptr(), scale.data_ptr(), out.data_ptr(), M,
+                                       h.size(1), _dt(h), _st()), "gather_scale_rows")
+    return out
+
+
+def combine_rows(y: torch.Tensor, where: torch.Tensor, n: int, top: int) -> torch.Tensor:
+    """``out[t] = sum_k y[where[t*top + k]]`` summed in fp32 in the order of ``k`` (int32 ``where``)."""
+    if not y.is_cuda:
+        return y[where.long()].float().view(n, top, -1).sum(1).to(y.dtype)
+    assert y.is_contiguous()
+    out = torch.empty(n, y.size(1), device=y.device, dtype=y.dtype)
+    _check(lib().hyb_combine_rows(y.data_ptr(), where.data_ptr(), out.data_ptr(), n, top, y.size(1), _dt(y), _st()),
+           "combine_rows")
+    return out
 
 
 def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
