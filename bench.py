@@ -153,8 +153,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-table", "reference-nccl"],
                     help="reference = byte-stock reference; reference-table = + injected partition-table entry for node counts it lacks; "
                          "reference-nccl = its data plane swapped for torch.distributed send/recv (baseline/nccl_connections.py)")
-    ap.add_argument("--family", default="", choices=["", "hybrid"],
-                    help="side benchmark: prefill/decode of the hybrid model family beside a transformer of the same size "
+    ap.add_argument("--family", default="", choices=["", "hybrid", "vudelix"],
+                    help="side benchmark: prefill/decode of the hybrid model family beside a transformer of the same size, or "
+                         "(vudelix) of its pre-norm design beside its sandwich design of the same width "
                          "(prints its own JSON line; the default workload is untouched)")
     ap.add_argument("--family-widths", default="1024,2048,4096")
     ap.add_argument("--model", default="Llama-3-8B")
@@ -577,7 +578,7 @@ def run_ours(args: argparse.Namespace) -> Dict[str, Any]:
 
 def main() -> None:
     args = parse_args()
-    if args.family == "hybrid":
+    if args.family:
         from mdi_llm_b200.utils.family_bench import run_family_compare
 
         sys.stdout.flush()
@@ -585,7 +586,7 @@ def main() -> None:
         os.dup2(2, 1)
         try:
             out = run_family_compare([int(w) for w in args.family_widths.split(",")], prompt_len=args.prompt_len if args.prompt_len != 448 else 2048,
-                                     steps=min(args.steps, 64), warmup=max(3, args.warmup))
+                                     steps=min(args.steps, 64), warmup=max(3, args.warmup), family=args.family)
         finally:
             sys.stdout.flush()
             os.dup2(saved, 1)

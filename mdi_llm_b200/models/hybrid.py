@@ -357,7 +357,8 @@ class MoEFF(nn.Module):
 
     The expert weights are stacked (``up [E, ff, C]``, ``down [E, C, ff]``) at load; the per-expert parameters the
     checkpoint names become views.  Few tokens (decoding) run two index-driven weight-streaming kernels; many tokens
-    are sorted by expert and run one pair of matrix products per expert that received any."""
+    are sorted by expert and run as two grouped matrix products (bf16: one vendor call each, group sizes stay on the
+    device; fp32: one product per expert that received any)."""
 
     gemv_max = 64  # token-expert pairs up to which the index-driven kernels are used
 
@@ -380,6 +381,7 @@ class MoEFF(nn.Module):
         for j in range(self.E):
             self.e_up[j].data, self.e_down[j].data = self.up[j], self.down[j]
         self.router32 = self.router.data.float().contiguous()
+        self.expert_ids = torch.arange(self.E, device=self.router.device)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         N, top = h.size(0), self.top
@@ -389,14 +391,9 @@ class MoEFF(nn.Module):
             return H.moe_gemv(h, idx, wt, self.up, self.down)
         flat = idx.view(-1).long()
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=self.E).tolist()
+        counts = (flat[:, None] == self.expert_ids[None, :]).sum(0)  # stays on the device
         xin = H.gather_scale_rows(h, (order // top).to(torch.int32), wt.view(-1)[order].contiguous())
-        y = torch.empty(N * top, h.size(1), device=h.device, dtype=h.dtype)
-        r = 0
-        for e, c in enumerate(counts):
-            if c:
-                y[r:r + c] = H.linear(H.relu2_(H.linear(xin[r:r + c], self.up[e])), self.down[e])
-                r += c
+        y = H.grouped_linear(H.relu2_(H.grouped_linear(xin, self.up, counts)), self.down, counts)
         where = torch.empty_like(order)
         where[order] = torch.arange(order.numel(), device=order.device)
         return H.combine_rows(y, where.to(torch.int32), N, top)

@@ -1012,13 +1012,16 @@ __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, cons
 // One block per (token, key/value head); warp w is query head g * rep + w.  A tile of 32 cached keys and values is
 // staged in shared memory as fp32 once and used by all heads of the group; lane j scores key j, the online softmax
 // and the weighted sum are fp32; the result is multiplied by sigmoid(gate) per head.  V <= 256.
+// With nsplit > 1 (few tokens: decoding) block z takes every nsplit-th tile and leaves its unnormalised sum, running
+// maximum and denominator in part_acc / part_ml; window_combine_kernel merges the shares and applies the gate.
 #define WT_TILE 32
 #define WT_MAXV 8
 template <typename T>
 __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ gate,
                                    long long g_stride, const T* __restrict__ cache, long long slot_stride,
                                    const int* __restrict__ meta, const int* __restrict__ tok_seq, T* __restrict__ out,
-                                   int H, int G, int D, int V, float scale, int window) {
+                                   int H, int G, int D, int V, float scale, int window, int nsplit,
+                                   float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ float sm[];
   int rep = H / G;
   float* qs = sm;                       // [rep][D]
@@ -1037,7 +1040,8 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
 #pragma unroll
   for (int c = 0; c < WT_MAXV; ++c) acc[c] = 0.f;
   float mx = -INFINITY, l = 0.f;
-  for (int j0 = lo; j0 <= pos; j0 += WT_TILE) {
+  __syncthreads();
+  for (int j0 = lo + (int)blockIdx.z * WT_TILE; j0 <= pos; j0 += WT_TILE * nsplit) {
     __syncthreads();
     for (int i = threadIdx.x; i < WT_TILE * D; i += blockDim.x) {
       int j = i / D, d = i - j * D;
@@ -1073,12 +1077,46 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
     }
   }
   int h = g * rep + w;
+  if (nsplit > 1) {
+    size_t row = ((size_t)blockIdx.z * gridDim.x + t) * H + h;
+#pragma unroll
+    for (int c = 0; c < WT_MAXV; ++c) {
+      int d = lane + 32 * c;
+      if (d < V) part_acc[row * V + d] = acc[c];
+    }
+    if (lane == 0) { part_ml[2 * row] = mx; part_ml[2 * row + 1] = l; }
+    return;
+  }
   float gt = gate ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
   float inv = gt / l;
 #pragma unroll
   for (int c = 0; c < WT_MAXV; ++c) {
     int d = lane + 32 * c;
     if (d < V) out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(acc[c] * inv);
+  }
+}
+
+// Merge of the key shares of window_attn_kernel: one block per (token, head).
+template <typename T>
+__global__ void window_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                      const T* __restrict__ gate, long long g_stride, T* __restrict__ out, int N, int H,
+                                      int V, int nsplit) {
+  int t = blockIdx.x, h = blockIdx.y;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[2 * (((size_t)s * N + t) * H + h)]);
+  float l = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    size_t row = ((size_t)s * N + t) * H + h;
+    l += part_ml[2 * row + 1] * expf(part_ml[2 * row] - M);
+  }
+  float gt = gate ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
+  for (int d = threadIdx.x; d < V; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      size_t row = ((size_t)s * N + t) * H + h;
+      a += part_acc[row * V + d] * expf(part_ml[2 * row] - M);
+    }
+    out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(a * gt / l);
   }
 }
 
@@ -1224,24 +1262,30 @@ int hyb_window_append(void* q, long long q_stride, const void* k, long long k_st
 
 int hyb_window_attn(const void* q, long long q_stride, const void* gate, long long g_stride, const void* cache,
                     long long slot_stride, const int* meta, const int* tok_seq, void* out, int N, int H, int G, int D,
-                    int V, float scale, int window, int dt, cudaStream_t st) {
+                    int V, float scale, int window, int nsplit, float* part_acc, float* part_ml, int dt,
+                    cudaStream_t st) {
   if (N == 0) return 0;
   int rep = G > 0 ? H / G : 0;
   if (rep < 1 || rep * G != H || rep > 32 || V > 32 * WT_MAXV) return -3;
+  if (nsplit < 1 || (nsplit > 1 && (!part_acc || !part_ml))) return -2;
   size_t smem = ((size_t)rep * D + (size_t)WT_TILE * (D + 1) + (size_t)WT_TILE * V) * sizeof(float);
   if (smem > 220 * 1024) return -3;
-  dim3 grid(N, G);
+  dim3 grid(N, G, nsplit), cgrid(N, H);
   cudaError_t e;
   if (dt == 0) {
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<bf16><<<grid, 32 * rep, smem, st>>>((const bf16*)q, q_stride, (const bf16*)gate, g_stride,
                                                            (const bf16*)cache, slot_stride, meta, tok_seq, (bf16*)out, H,
-                                                           G, D, V, scale, window);
+                                                           G, D, V, scale, window, nsplit, part_acc, part_ml);
+    if (nsplit > 1)
+      window_combine_kernel<bf16><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit);
   } else {
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<float><<<grid, 32 * rep, smem, st>>>((const float*)q, q_stride, (const float*)gate, g_stride,
                                                             (const float*)cache, slot_stride, meta, tok_seq, (float*)out,
-                                                            H, G, D, V, scale, window);
+                                                            H, G, D, V, scale, window, nsplit, part_acc, part_ml);
+    if (nsplit > 1)
+      window_combine_kernel<float><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit);
   }
   return (int)cudaGetLastError();
 }

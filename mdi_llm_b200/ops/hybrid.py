@@ -28,7 +28,7 @@ from . import build as _build
 
 __all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
            "headmajor_gate", "softcap", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
-           "rotary_inv_freq", "scaled_inv_freq", "linear_f32", "window_append", "window_attn", "head_gate", "relu2_",
+           "rotary_inv_freq", "scaled_inv_freq", "linear_f32", "grouped_linear", "window_append", "window_attn", "head_gate", "relu2_",
            "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows"]
 
 
@@ -64,7 +64,7 @@ def lib() -> ctypes.CDLL:
     h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, vp]
     h.hyb_gelu_rows.argtypes = [vp, i64, i32, i32, vp]
     h.hyb_window_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
-    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp]
+    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, vp]
     h.hyb_head_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_token_side_gate.argtypes = [vp, i64, vp, i64, i32, vp, vp, i32, i32, i32, vp]
     h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, vp]
@@ -164,6 +164,21 @@ def linear_f32(x: torch.Tensor, w32: torch.Tensor) -> torch.Tensor:
     if x.is_cuda and torch.backends.cuda.matmul.allow_tf32:
         raise HybridOpsError("TF32 matrix products are on; router logits are fp32")
     return F.linear(x.float(), w32)
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """Rows of ``x [M, K]`` sorted by group, ``counts [E]`` rows per group (on the device): row ``i`` of group ``e`` times
+    ``w[e].T`` (``w [E, out, K]``).  bf16 on CUDA is one vendor grouped matrix product with no host synchronisation;
+    anything else (fp32 must stay true fp32, CPU) is one product per non-empty group."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and hasattr(F, "grouped_mm"):
+        return F.grouped_mm(x, w.transpose(1, 2), offs=counts.cumsum(0).to(torch.int32))
+    out = torch.empty(x.size(0), w.size(1), device=x.device, dtype=x.dtype)
+    r = 0
+    for e, c in enumerate(counts.tolist()):
+        if c:
+            out[r:r + c] = linear(x[r:r + c], w[e])
+            r += c
+    return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -441,11 +456,13 @@ def window_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: O
 
 
 def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor, plan: BatchPlan, H: int, G: int, D: int,
-                V: int, scale: float, window: int) -> torch.Tensor:
+                V: int, scale: float, window: int, split: int = 0) -> torch.Tensor:
     """Softmax attention of every token over the cached keys of its slot that are not later than it and (``window > 0``)
     fewer than ``window`` positions back; query head ``h`` reads key/value head ``h // (H/G)``.  Each head's output is
     multiplied by ``sigmoid(g[token, h])`` when ``g`` is given.  Returns ``[N, H*V]``.  The form for one-token steps and
-    short portions: one block per token and key/value head, the cache tile shared by the group's query heads."""
+    short portions: one block per token and key/value head, the cache tile shared by the group's query heads.
+    ``split`` (CUDA): key shares per token, 0 = chosen from the batch shape and the window alone, so that a captured
+    step stays valid while contexts grow."""
     N = q.size(0)
     if not q.is_cuda:
         out = torch.empty(N, H * V, dtype=q.dtype)
@@ -467,9 +484,17 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
             out[r0:r0 + n] = o.reshape(n, H * V).to(q.dtype)
         return out
     out = torch.empty(N, H * V, device=q.device, dtype=q.dtype)
+    blocks = N * G
+    tiles = (window + 31) // 32 if window > 0 else 16
+    nsplit = split or (1 if blocks >= 2 * _SM_TARGET else max(1, min(32, tiles, (2 * _SM_TARGET + blocks - 1) // blocks)))
+    pa = pm = None
+    if nsplit > 1:
+        pa = torch.empty(nsplit, N, H, V, device=q.device, dtype=torch.float32)
+        pm = torch.empty(nsplit, N, H, 2, device=q.device, dtype=torch.float32)
     _check(lib().hyb_window_attn(q.data_ptr(), _rows(q)[0], None if g is None else g.data_ptr(),
                                  0 if g is None else _rows(g)[0], cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
-                                 plan.tok_seq.data_ptr(), out.data_ptr(), N, H, G, D, V, float(scale), int(window),
+                                 plan.tok_seq.data_ptr(), out.data_ptr(), N, H, G, D, V, float(scale), int(window), nsplit,
+                                 None if pa is None else pa.data_ptr(), None if pm is None else pm.data_ptr(),
                                  _dt(q), _st()), "window_attn")
     return out
 

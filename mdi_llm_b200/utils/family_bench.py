@@ -11,6 +11,10 @@ sized to the same parameter count) are built with random weights.  Measured with
   and FLOP/s against the measured peaks, beside the transformer's attention kernels on the same token counts.
 
 An L2 flush (a write larger than L2) separates timed iterations of the single-kernel measurements.
+
+``bench.py --family vudelix`` measures the pre-norm design of the family (windowed grouped-query attention, gated
+delta rule, mixture-of-experts and dense feed-forwards, per-layer token embedding) the same way, beside the sandwich
+design of the same width as the closest existing model, with its own kernels one by one.
 """
 from __future__ import annotations
 
@@ -20,7 +24,22 @@ from typing import Any, Callable, Dict, List
 
 import torch
 
-__all__ = ["run_family_compare", "hybrid_bench_config"]
+__all__ = ["run_family_compare", "hybrid_bench_config", "vudelix_bench_config"]
+
+
+def vudelix_bench_config(width: int, window: int = 1024) -> Dict[str, Any]:
+    """4 layers: delta + dense, attention + experts, delta + experts, attention + dense.  Two of eight experts of
+    width ``2 * width`` per token, so a token's feed-forward work equals the dense ``4 * width`` one."""
+    h = width // 128
+    dense = {"kind": "dense", "ff": 4 * width}
+    moe = {"kind": "moe", "expert": {"ff": 2 * width}, "router": {"experts": 8, "top": 2}}
+    att = {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window},
+           "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    delta = {"heads": h, "kv_heads": max(1, h // 2), "dim": 128, "vdim": 128, "conv": 4}
+    layers = [{"type": "channel_delta", "mixer": dict(delta), "mlp": dense}, {"type": "attention", "mixer": dict(att), "mlp": moe},
+              {"type": "channel_delta", "mixer": dict(delta), "mlp": moe}, {"type": "attention", "mixer": dict(att), "mlp": dense}]
+    return {"architecture": "Vudelix", "vocab": 32000, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "token_side": {"dim": 64}}
 
 
 def hybrid_bench_config(width: int) -> Dict[str, Any]:
@@ -64,13 +83,13 @@ def _peaks() -> Dict[str, float]:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
-def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int) -> Dict[str, Any]:
+def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int, design: str = "hybrid") -> Dict[str, Any]:
     from ..models.config import HybridConfig
     from ..models.hybrid import HybridLM
     from ..parallel.hybrid_runner import HybridRunner
 
     dev = torch.device("cuda")
-    cfg = HybridConfig.from_dict(hybrid_bench_config(width))
+    cfg = HybridConfig.from_dict(hybrid_bench_config(width) if design == "hybrid" else vudelix_bench_config(width))
     model = HybridLM(cfg, {}).init_random(dev, torch.bfloat16, seed=1)
     params = sum(p.numel() for p in model.tensor_map().values())
     out: Dict[str, Any] = {"params_m": round(params / 1e6, 1), "layer_params_m": round((params - model.embed.numel()) / 1e6, 1)}
@@ -98,8 +117,76 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int) ->
         out[f"decode_tok_s_b{b}"] = round(b / ms * 1e3, 1)
         out[f"decode_ms_b{b}"] = round(ms, 4)
         del r
-    out["kernels"] = _hybrid_kernels(model, prompt_len, batch)
+    out["kernels"] = (_hybrid_kernels if design == "hybrid" else _vudelix_kernels)(model, prompt_len, batch)
     return out
+
+
+def _vudelix_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
+    """The pre-norm design's own kernels alone, on the prompt shape and on the decode shape (see ``_hybrid_kernels``)."""
+    from ..ops import hybrid as H
+
+    pk = _peaks()
+    dev, dt = model.device, model.dtype
+    C = model.config.width
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def rec(name: str, phase: str, ms: float, nbytes: float, flops: float) -> None:
+        rows.append({"kernel": name, "phase": phase, "ms": round(ms, 4), "gb_s": round(nbytes / ms / 1e6, 1),
+                     "tflops": round(flops / ms / 1e9, 2),
+                     "frac_of_roofline": round(max(nbytes / ms / 1e6 / pk["hbm_gbs"], flops / ms / 1e9 / pk["bf16_tflops"]), 4),
+                     "peaks": pk["source"]})
+
+    att, moe = model.blocks[1].mix, model.blocks[1].mlp
+    Hh, G, D, V, W = att.H, att.G, att.D, att.V, att.window
+    for phase, lengths, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [T] * batch)):
+        n_seq, N = len(lengths), sum(lengths)
+        pool = model.new_pool(n_seq, T + 8)
+        plan = H.BatchPlan.make(lengths, list(range(n_seq)), starts, dev)
+        cache = pool.runs[1]["cache"]
+        cache.normal_()
+        h = torch.randn(N, C, device=dev).to(dt)
+        p = H.linear(h, att.w_in)
+        q, g = att.col(p, "q"), att.col(p, "g")
+        pairs = sum(min(W, s + i + 1) if W else s + i + 1 for n, s in zip(lengths, starts) for i in range(n))
+        ms = _time(lambda: H.window_append(q, att.col(p, "k"), att.col(p, "v"), att.inv_freq, cache, plan, Hh, G, D, V,
+                                           att.nrot, 1e-6), 5, 3, flush)
+        rec("window_append", phase, ms, 2.0 * N * (2 * Hh * D + 2 * G * (D + V)), 0.0)
+        if phase == "prefill":
+            ms = _time(lambda: H.head_gate(att._banded(q, cache, plan), g), 5, 3, flush)
+            rec("window_attn_banded(gemm+softmax)", phase, ms, 2.0 * N * (Hh * (D + V) + G * (D + V)), 2.0 * Hh * pairs * (D + V))
+            nb = min(N, att.query_block)
+            s32 = torch.randn(Hh, nb, nb + W - 1, device=dev)
+            ms = _time(lambda: H.causal_softmax(s32, N - nb, att.scale, dt, window=W, key0=N - nb - W + 1), 5, 3, flush)
+            rec("causal_softmax[window]", phase, ms, s32.numel() * 6.0, 0.0)
+            del s32
+        else:
+            ms = _time(lambda: H.window_attn(q, g, cache, plan, Hh, G, D, V, att.scale, W), 5, 3, flush)
+            keys = sum(min(W, s + 1) if W else s + 1 for s in starts)
+            rec("window_attn", phase, ms, 2.0 * G * keys * (D + V) + 2.0 * N * Hh * (D + V), 2.0 * Hh * pairs * (D + V))
+        z = H.linear_f32(h, moe.router32)
+        ms = _time(lambda: H.router_topk(z, moe.top), 5, 3, flush)
+        rec("router_topk", phase, ms, 4.0 * N * (moe.E + 2 * moe.top), 0.0)
+        ms = _time(lambda: moe(h), 5, 3, flush)
+        wbytes = 2.0 * 2 * C * moe.ff * min(moe.E, N * moe.top)
+        rec("moe_experts[index-driven]" if N * moe.top <= moe.gemv_max else "moe_experts[grouped gemm]", phase, ms,
+            wbytes + 2.0 * N * C * (1 + moe.top), 4.0 * N * moe.top * C * moe.ff)
+        ff = model.blocks[0].mlp
+        ms = _time(lambda: ff(h), 5, 3, flush)
+        rec("dense_ff(gemm+gelu)", phase, ms, 2.0 * 2 * C * ff.up.size(0) + 4.0 * N * C, 4.0 * N * C * ff.up.size(0))
+        side = model.blocks[0].side
+        zs = H.linear(h, side.gate)
+        tok = torch.randint(0, model.config.vocab, (N,), device=dev, dtype=torch.int32)
+        ms = _time(lambda: H.token_side_gate(zs, model.side_embed, tok, 0), 5, 3, flush)
+        rec("token_side_gate", phase, ms, 2.0 * N * 3 * side.dim, 0.0)
+        x = torch.randn(N, C, device=dev)
+        ms = _time(lambda: H.norm_rows(x, model.blocks[0].norm1.w, None, 1e-6, "rms", dt), 5, 3, flush)
+        rec("rms_norm", phase, ms, N * C * 6.0, 0.0)
+        y = torch.randn(N, C, device=dev).to(dt)
+        ms = _time(lambda: H.norm_accumulate(x, y, None, None, 1e-6, "none", 0.5), 5, 3, flush)
+        rec("scaled_residual_add", phase, ms, N * C * 10.0, 0.0)
+        del pool
+    return rows
 
 
 def _hybrid_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
@@ -229,9 +316,20 @@ def _transformer(width: int, prompt_len: int, steps: int, warmup: int, target_pa
     return out
 
 
-def run_family_compare(widths: List[int], prompt_len: int = 2048, batch: int = 8, steps: int = 64, warmup: int = 8) -> Dict[str, Any]:
+def run_family_compare(widths: List[int], prompt_len: int = 2048, batch: int = 8, steps: int = 64, warmup: int = 8,
+                       family: str = "hybrid") -> Dict[str, Any]:
     torch.backends.cuda.matmul.allow_tf32 = False
     results = []
+    if family == "vudelix":
+        for w in widths:
+            new = _hybrid(w, prompt_len, batch, steps, warmup, "vudelix")
+            torch.cuda.empty_cache()
+            old = _hybrid(w, prompt_len, batch, steps, warmup, "hybrid")
+            torch.cuda.empty_cache()
+            results.append({"width": w, "vudelix": new, "hybrid": old})
+        return {"metric": "family_compare", "family": "vudelix", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+                "decode_batch": batch, "steps": steps, "warmup": warmup, "l2": "flushed between single-kernel timings",
+                "results": results}
     for w in widths:
         hy = _hybrid(w, prompt_len, batch, steps, warmup)
         torch.cuda.empty_cache()

@@ -307,6 +307,21 @@ def test_keys_just_inside_and_outside_the_window_and_far_back(dev, W, monkeypatc
     assert (got[0] - v[p - W, 0]).abs().max() > 0.2
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_key_shares_of_the_decode_form_agree(dtype):
+    G, rep, D, V, S, W = 2, 3, 8, 6, 160, 70
+    k, v, cache = _sharp_case(("cuda", dtype), W)
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(3, G * rep * D, generator=g).to(device="cuda", dtype=dtype)
+    gate = torch.randn(3, G * rep, generator=g).to(device="cuda", dtype=dtype)
+    plan = BatchPlan.make([1, 1, 1], [1, 1, 1], [3, 69, 159], torch.device("cuda"))
+    one = H.window_attn(q, gate, cache, plan, G * rep, G, D, V, 0.8, W, split=1)
+    for split in (0, 2, 5):  # 5 shares: some get no tile at all for the short context
+        got = H.window_attn(q, gate, cache, plan, G * rep, G, D, V, 0.8, W, split=split)
+        assert (got.float() - one.float()).abs().max() < (1e-5 if dtype == torch.float32 else 0.02), split
+
+
 @pytest.mark.parametrize("dev", DEVICES)
 def test_append_rotates_normalises_and_writes_the_cache(dev):
     device, dtype = dev
