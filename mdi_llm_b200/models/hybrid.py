@@ -297,7 +297,7 @@ class WindowAttention(nn.Module, _Fused):
 
     tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
     expand_from = 64   # a step whose every sequence brings at least this many tokens runs as banded matrix products
-    query_block = 512  # query rows per band
+    query_block = 1024  # query rows per band
 
     def __init__(self, width: int, m: Dict[str, Any], eps: float) -> None:
         super().__init__()

@@ -170,7 +170,8 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> to
     """Rows of ``x [M, K]`` sorted by group, ``counts [E]`` rows per group (on the device): row ``i`` of group ``e`` times
     ``w[e].T`` (``w [E, out, K]``).  bf16 on CUDA is one vendor grouped matrix product with no host synchronisation;
     anything else (fp32 must stay true fp32, CPU) is one product per non-empty group."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and hasattr(F, "grouped_mm"):
+    aligned = x.size(1) % 8 == 0 and w.size(1) % 8 == 0 and x.is_contiguous() and w.is_contiguous()  # 16-byte rows
+    if x.is_cuda and x.dtype == torch.bfloat16 and aligned and hasattr(F, "grouped_mm"):
         return F.grouped_mm(x, w.transpose(1, 2), offs=counts.cumsum(0).to(torch.int32))
     out = torch.empty(x.size(0), w.size(1), device=x.device, dtype=x.dtype)
     r = 0
