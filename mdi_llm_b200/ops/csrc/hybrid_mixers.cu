@@ -1180,44 +1180,108 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ wrow, const float
   return warp_sum(a);
 }
 
-// act[p, f] = relu(up[e_p][f, :] . (w_p * h[t_p, :]))^2 for pair p = (token, slot k); grid (pairs, ceil(ff / 32)).
+// Experts by index for few tokens.  A pair p = (token, choice k) names expert idx[p] and score wt[p].  One block owns
+// 32 output rows of ONE expert and serves every pair that chose it, MOE_PCH pairs at a time, so an expert's weights
+// cross the memory system once however many pairs share it; experts nobody chose cost one scan of idx.
+//   MODE 0 (up):   y[p, f] = relu(w[e][f, :] . round_T(wt[p] * x[p / top, :]))^2     x in T, K = width
+//   MODE 1 (down): y[p, c] = w[e][c, :] . a[p, :]                                    a fp32, K = ff
 #define MOE_ROWS 32
-template <typename T>
-__global__ void moe_up_kernel(const T* __restrict__ h, long long h_stride, const int* __restrict__ idx,
-                              const float* __restrict__ wt, const T* __restrict__ up, float* __restrict__ act, int top,
-                              int C, int ff) {
-  extern __shared__ float sm[];
-  int p = blockIdx.x, t = p / top;
-  int e = idx[p];
-  float w = wt[p];
-  for (int c = threadIdx.x; c < C; c += blockDim.x) sm[c] = to_f(from_f<T>(w * to_f(h[(size_t)t * h_stride + c])));
-  __syncthreads();
+#define MOE_PCH 4
+template <typename T, int MODE>
+__global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_stride, const int* __restrict__ idx,
+                                 const float* __restrict__ wt, const T* __restrict__ w, float* __restrict__ y, int P,
+                                 int top, int K, int R, int pch) {
+  extern __shared__ float sm[];  // [pch][K]
+  __shared__ int match[MOE_PCH];
+  __shared__ int s_cnt, s_next;
+  int e = blockIdx.x;
   int lane = threadIdx.x & 31, wp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const T* we = up + (size_t)e * ff * C;
-  for (int r = wp; r < MOE_ROWS; r += nw) {
-    int f = blockIdx.y * MOE_ROWS + r;
-    if (f >= ff) break;
-    float a = dot_row(we + (size_t)f * C, sm, C, lane);
-    if (lane == 0) { a = fmaxf(a, 0.f); act[(size_t)p * ff + f] = a * a; }
+  const T* we = w + (size_t)e * R * K;
+  if (threadIdx.x == 0) s_next = 0;
+  __syncthreads();
+  while (true) {
+    if (threadIdx.x == 0) {
+      int c = 0, p = s_next;
+      for (; p < P && c < pch; ++p)
+        if (idx[p] == e) match[c++] = p;
+      s_cnt = c;
+      s_next = p;
+    }
+    __syncthreads();
+    int cnt = s_cnt;
+    if (cnt == 0) return;
+    for (int m = 0; m < cnt; ++m) {
+      int p = match[m];
+      if (MODE == 0) {
+        const T* x = (const T*)xin + (size_t)(p / top) * x_stride;
+        float sc = wt[p];
+        for (int c = threadIdx.x; c < K; c += blockDim.x) sm[m * K + c] = to_f(from_f<T>(sc * to_f(x[c])));
+      } else {
+        const float* x = (const float*)xin + (size_t)p * x_stride;
+        for (int c = threadIdx.x; c < K; c += blockDim.x) sm[m * K + c] = x[c];
+      }
+    }
+    __syncthreads();
+    for (int r = wp; r < MOE_ROWS; r += nw) {
+      int f = blockIdx.y * MOE_ROWS + r;
+      if (f >= R) break;
+      const T* wrow = we + (size_t)f * K;
+      float acc[MOE_PCH];
+#pragma unroll
+      for (int m = 0; m < MOE_PCH; ++m) acc[m] = 0.f;
+      if ((K & 7) == 0) {
+        // four 16-byte weight loads in flight per lane before any of them is used
+        for (int c0 = lane * 8; c0 < K; c0 += 1024) {
+          float wv[4][8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (c0 + 256 * u < K) load8(wrow + c0 + 256 * u, wv[u]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            int c = c0 + 256 * u;
+            if (c < K) {
+#pragma unroll
+              for (int m = 0; m < MOE_PCH; ++m)
+                if (m < cnt) {  // two 16-byte shared loads per lane: no bank conflicts
+                  const float4* xv = reinterpret_cast<const float4*>(sm + (size_t)m * K + c);
+                  float4 x0 = xv[0], x1 = xv[1];
+                  acc[m] += wv[u][0] * x0.x + wv[u][1] * x0.y + wv[u][2] * x0.z + wv[u][3] * x0.w + wv[u][4] * x1.x +
+                            wv[u][5] * x1.y + wv[u][6] * x1.z + wv[u][7] * x1.w;
+                }
+            }
+          }
+        }
+      } else {
+        for (int c = lane; c < K; c += 32) {
+          float wv = to_f(wrow[c]);
+#pragma unroll
+          for (int m = 0; m < MOE_PCH; ++m)
+            if (m < cnt) acc[m] += wv * sm[m * K + c];
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MOE_PCH; ++m) {
+        if (m < cnt) {
+          float v = warp_sum(acc[m]);
+          if (lane == 0) {
+            if (MODE == 0) { v = fmaxf(v, 0.f); v = v * v; }
+            y[(size_t)match[m] * R + f] = v;
+          }
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 
-// out[t, c] = sum_k down[e_(t,k)][c, :] . act[(t,k), :]; grid (tokens, ceil(C / 32)).
+// out[t, c] = sum_k y[t * top + k, c], summed in the order of k.
 template <typename T>
-__global__ void moe_down_kernel(const float* __restrict__ act, const int* __restrict__ idx, const T* __restrict__ down,
-                                T* __restrict__ out, int top, int C, int ff) {
-  extern __shared__ float sm[];
+__global__ void moe_sum_kernel(const float* __restrict__ y, T* __restrict__ out, int top, int C) {
   int t = blockIdx.x;
-  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) sm[i] = act[(size_t)t * top * ff + i];
-  __syncthreads();
-  int lane = threadIdx.x & 31, wp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int r = wp; r < MOE_ROWS; r += nw) {
-    int c = blockIdx.y * MOE_ROWS + r;
-    if (c >= C) break;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float a = 0.f;
-    for (int k = 0; k < top; ++k)
-      a += dot_row(down + ((size_t)idx[(size_t)t * top + k] * C + c) * ff, sm + k * ff, ff, lane);
-    if (lane == 0) out[(size_t)t * C + c] = from_f<T>(a);
+    for (int k = 0; k < top; ++k) a += y[((size_t)t * top + k) * C + c];
+    out[(size_t)t * C + c] = from_f<T>(a);
   }
 }
 
@@ -1320,37 +1384,45 @@ int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, 
   return (int)cudaGetLastError();
 }
 
-int hyb_moe_up(const void* h, long long h_stride, const int* idx, const float* wt, const void* up, float* act, int N,
-               int top, int C, int ff, int dt, cudaStream_t st) {
-  if (N == 0) return 0;
-  size_t smem = (size_t)C * sizeof(float);
+}  // extern "C"
+
+template <typename T, int MODE>
+static int launch_moe_pairs(const void* x, long long x_stride, const int* idx, const float* wt, const void* w, float* y,
+                            int P, int top, int K, int R, int E, cudaStream_t st) {
+  // shared memory only for the pairs there can be, and at most 64 KB while more than one pair is staged: three
+  // blocks per SM keep more weight loads in flight than one block that serves four pairs at once
+  int pch = P < MOE_PCH ? P : MOE_PCH;
+  while (pch > 1 && (size_t)pch * K * sizeof(float) > 64 * 1024) --pch;
+  size_t smem = (size_t)pch * K * sizeof(float);
   if (smem > 200 * 1024) return -3;
-  dim3 grid(N * top, (ff + MOE_ROWS - 1) / MOE_ROWS);
-  cudaError_t e;
-  if (dt == 0) {
-    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-    moe_up_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)h, h_stride, idx, wt, (const bf16*)up, act, top, C, ff);
-  } else {
-    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-    moe_up_kernel<float><<<grid, 256, smem, st>>>((const float*)h, h_stride, idx, wt, (const float*)up, act, top, C, ff);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_pairs_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
   }
+  dim3 grid(E, (R + MOE_ROWS - 1) / MOE_ROWS);
+  moe_pairs_kernel<T, MODE><<<grid, 256, smem, st>>>(x, x_stride, idx, wt, (const T*)w, y, P, top, K, R, pch);
   return (int)cudaGetLastError();
 }
 
-int hyb_moe_down(const float* act, const int* idx, const void* down, void* out, int N, int top, int C, int ff, int dt,
-                 cudaStream_t st) {
+extern "C" {
+
+// act [N*top, ff] fp32 = squared-ReLU of the chosen experts' up projections of the score-weighted token.
+int hyb_moe_up(const void* h, long long h_stride, const int* idx, const float* wt, const void* up, float* act, int N,
+               int top, int C, int ff, int E, int dt, cudaStream_t st) {
   if (N == 0) return 0;
-  size_t smem = (size_t)top * ff * sizeof(float);
-  if (smem > 200 * 1024) return -3;
-  dim3 grid(N, (C + MOE_ROWS - 1) / MOE_ROWS);
-  cudaError_t e;
-  if (dt == 0) {
-    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-    moe_down_kernel<bf16><<<grid, 256, smem, st>>>(act, idx, (const bf16*)down, (bf16*)out, top, C, ff);
-  } else {
-    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-    moe_down_kernel<float><<<grid, 256, smem, st>>>(act, idx, (const float*)down, (float*)out, top, C, ff);
-  }
+  if (dt == 0) return launch_moe_pairs<bf16, 0>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
+  return launch_moe_pairs<float, 0>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
+}
+
+// out [N, C] = sum over a token's choices of the expert's down projection of act; ypair [N*top, C] fp32 is scratch.
+int hyb_moe_down(const float* act, const int* idx, const void* down, float* ypair, void* out, int N, int top, int C,
+                 int ff, int E, int dt, cudaStream_t st) {
+  if (N == 0) return 0;
+  int rc = dt == 0 ? launch_moe_pairs<bf16, 1>(act, ff, idx, nullptr, down, ypair, N * top, top, ff, C, E, st)
+                   : launch_moe_pairs<float, 1>(act, ff, idx, nullptr, down, ypair, N * top, top, ff, C, E, st);
+  if (rc) return rc;
+  HYB_DISPATCH(dt, (moe_sum_kernel<bf16><<<N, 256, 0, st>>>(ypair, (bf16*)out, top, C)),
+               (moe_sum_kernel<float><<<N, 256, 0, st>>>(ypair, (float*)out, top, C)));
   return (int)cudaGetLastError();
 }
 

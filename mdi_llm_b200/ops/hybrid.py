@@ -68,8 +68,8 @@ def lib() -> ctypes.CDLL:
     h.hyb_head_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_token_side_gate.argtypes = [vp, i64, vp, i64, i32, vp, vp, i32, i32, i32, vp]
     h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, vp]
-    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
-    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
     h.hyb_gather_scale_rows.argtypes = [vp, i64, vp, vp, vp, i32, i32, i32, vp]
     h.hyb_combine_rows.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
     h.hyb_headmajor_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
@@ -521,7 +521,8 @@ def router_topk(z: torch.Tensor, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
 
 def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
     """``sum_k down[e_k] relu(up[e_k] (w_k h))^2`` per token, experts read by index (``up [E, ff, C]``, ``down [E, C, ff]``).
-    The form for few tokens: two weight-streaming kernels, no grouping and no host synchronisation."""
+    The form for few tokens: weight-streaming kernels in which one block serves every token that chose its expert
+    (an expert's weights are read once per step), no sorting and no host synchronisation."""
     N, C = h.shape
     E, ff, _ = up.shape
     top = idx.size(1)
@@ -536,11 +537,12 @@ def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Ten
         return out.to(h.dtype)
     assert up.is_contiguous() and down.is_contiguous() and idx.is_contiguous() and wt.is_contiguous()
     act = torch.empty(N, top, ff, device=h.device, dtype=torch.float32)
+    ypair = torch.empty(N, top, C, device=h.device, dtype=torch.float32)
     out = torch.empty(N, C, device=h.device, dtype=h.dtype)
     _check(lib().hyb_moe_up(h.data_ptr(), _rows(h)[0], idx.data_ptr(), wt.data_ptr(), up.data_ptr(), act.data_ptr(), N, top,
-                            C, ff, _dt(h), _st()), "moe_up")
-    _check(lib().hyb_moe_down(act.data_ptr(), idx.data_ptr(), down.data_ptr(), out.data_ptr(), N, top, C, ff, _dt(h), _st()),
-           "moe_down")
+                            C, ff, E, _dt(h), _st()), "moe_up")
+    _check(lib().hyb_moe_down(act.data_ptr(), idx.data_ptr(), down.data_ptr(), ypair.data_ptr(), out.data_ptr(), N, top, C,
+                              ff, E, _dt(h), _st()), "moe_down")
     return out
 
 

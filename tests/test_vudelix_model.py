@@ -103,10 +103,11 @@ def all_rows(n):
 
 # ---- each mechanism alone -----------------------------------------------------------------------------------
 @pytest.mark.parametrize("dev", DEVICES)
-@pytest.mark.parametrize("case", ["attention", "attention_wide", "delta", "moe", "side", "no_side_no_mult"])
+@pytest.mark.parametrize("case", ["attention", "attention_wide", "attention_unbounded", "delta", "moe", "side", "no_side_no_mult"])
 def test_each_mechanism_alone(dev, case):
     bare = lambda spec: {**copy.deepcopy(spec), "mlp": None}
-    d = {"attention": cfg_dict([bare(ATT)], side=0), "attention_wide": cfg_dict([bare(ATT_WIDE)], side=0),
+    plain = {"type": "attention", "mlp": None, "mixer": {"heads": 1, "kv_heads": 1, "dim": 6, "vdim": 4, "scale": 0.9}}
+    d = {"attention": cfg_dict([bare(ATT)], side=0), "attention_unbounded": cfg_dict([plain, plain], side=0), "attention_wide": cfg_dict([bare(ATT_WIDE)], side=0),
          "delta": cfg_dict([DELTA_BARE], side=0), "moe": cfg_dict([{**copy.deepcopy(DELTA_BARE), "mlp": MOE}], side=0),
          "side": cfg_dict([DELTA_BARE], side=5), "no_side_no_mult": cfg_dict([ATT_WIDE], side=0, mult=1.0)}[case]
     d, m = build(d, dev)
